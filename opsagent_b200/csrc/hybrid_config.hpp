@@ -2,9 +2,12 @@
 // attention (a compressed key/value cache), a gated delta rule with per-channel decay, a Mamba-2 state-space layer, or windowed attention
 // over cached keys and values (sliding window with optional kept first tokens, one or two score maps per head, optional sink, output gate,
 // optionally reading another layer's cache), each beside a routed mixture-of-experts feed-forward, with an optional looped block that
-// re-injects the embedding.  Two designs are registered: "Ratasun" (one weight-only layer norm per layer, sigmoid group-limited router, SwiGLU
-// experts) and "Zurevik" (two RMS norms per layer, softmax over the chosen router logits, squared-ReLU experts, scaled embedding, soft-capped
-// logits).  Every size and constant is read from the checkpoint folder's config.json; nothing here is specific to one checkpoint.
+// re-injects the embedding.  Three designs are registered: "Ratasun" (one weight-only layer norm per layer, sigmoid group-limited router, SwiGLU
+// experts), "Zurevik" (two RMS norms per layer, softmax over the chosen router logits, squared-ReLU experts, scaled embedding, soft-capped
+// logits) and "Rofizen" (norm after the sum: x <- norm(alpha x + sublayer(x)), mixer and feed-forward in sequence; mixers: gated linear
+// attention with a decay per key channel, retention with a fixed decay per head and rotate-half rotary, or causal soft-capped attention with
+// a distance penalty beside an xLSTM matrix memory; feed-forward: dense squared-ReLU, or SwiGLU experts chosen by a table of token ids plus
+// a gated shared expert).  Every size and constant is read from the checkpoint folder's config.json; nothing here is specific to one checkpoint.
 #pragma once
 #include <cstdio>
 #include <fstream>
@@ -17,9 +20,23 @@
 
 namespace oa {
 
-enum HyMixer : int { HY_LATENT_ATTENTION = 0, HY_CHANNEL_DELTA = 1, HY_MAMBA2 = 2, HY_WINDOW_ATTENTION = 3 };
+enum HyMixer : int { HY_LATENT_ATTENTION = 0, HY_CHANNEL_DELTA = 1, HY_MAMBA2 = 2, HY_WINDOW_ATTENTION = 3, HY_LINEAR_ATTENTION = 4, HY_ATTENTION_BESIDE_MEMORY = 5 };
 enum HyNorm : int { HY_LAYER_NORM = 0, HY_RMS_NORM = 1 };
-enum HyRouterKind : int { HY_ROUTER_SIGMOID_GROUPS = 0, HY_ROUTER_SOFTMAX_CHOSEN = 1 };   // weights: sigmoid scores renormalised and scaled / softmax over the chosen logits
+enum HyRouterKind : int { HY_ROUTER_SIGMOID_GROUPS = 0, HY_ROUTER_SOFTMAX_CHOSEN = 1, HY_ROUTER_TOKEN_TABLE = 2 };   // weights: sigmoid scores renormalised and scaled / softmax over the chosen logits / a table row per token id, 1 / top each
+// linear-attention recurrences over an fp32 state S[dim, vdim] per head, o_t = S_t^T q_t:
+//   channel decay: S_t = diag(a_t) S_(t-1) + k_t v_t^T, a_t = sigmoid(z_t)^(1 / tau) per key channel from a low-rank projection (gated linear attention)
+//   head decay:    S_t = decay_h S_(t-1) + k_t v_t^T with a fixed decay per head, rotate-half rotary on q and k (retention)
+//   matrix memory: S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k_t v_t^T with log gates i, f, a running maximum m and a normaliser n (xLSTM's mLSTM)
+enum HyLinearKind : int { HY_LIN_CHANNEL_DECAY = 0, HY_LIN_HEAD_DECAY = 1, HY_LIN_MATRIX_MEMORY = 2 };
+enum HyLinearNorm : int { HY_LIN_NORM_HEAD_WEIGHT = 0, HY_LIN_NORM_NONE = 1, HY_LIN_NORM_ALL_WEIGHT = 2 };   // weight of the per-head RMS norm: [vdim] shared by heads / none / [heads * vdim]
+
+struct HyLinear {
+    int kind = HY_LIN_CHANNEL_DECAY, heads = 0, dim = 0, vdim = 0;
+    float tau = 1.f, gate_cap = 0.f, rot_base = 10000.f; int rot_dims = 0;
+    std::vector<float> decay;             // head decay: one per head
+    int norm = HY_LIN_NORM_HEAD_WEIGHT, gate_silu = 1;      // output gate: silu (1) or sigmoid (0) of a projection, per channel
+    bool q_scaled = true, k_scaled = false;                  // dim^-1/2 on q, or on k (after the rotation)
+};
 enum HyExpertAct : int { HY_EXPERT_SWIGLU = 0, HY_EXPERT_RELU2 = 1 };                       // down(silu(gate x) * up x) / down(relu(up x)^2)
 enum HyGate : int { HY_GATE_NONE = 0, HY_GATE_CHANNEL = 1, HY_GATE_HEAD = 2 };
 
@@ -28,6 +45,8 @@ struct HyMoe {
     int experts = 0, top = 0, groups = 1, keep = 1, ff = 0;
     float scale = 1.f;
     int router = HY_ROUTER_SIGMOID_GROUPS, act = HY_EXPERT_SWIGLU;
+    bool dense = false;                   // one feed-forward for every token (no router, no experts): down(act(up h)), width ff
+    int shared_ff = 0;                    // > 0: a shared expert of this width runs for every token, times sigmoid(w_sg . h)
 };
 
 struct HyLayer {
@@ -41,8 +60,12 @@ struct HyLayer {
     // head, out = a1 - lambda a2, unit RMS per head, times 1 - diff); position i sees j <= i with i - j < window or j < keep_first; qk_norm: RMS
     // norm of every query / key map with a weight shared by heads and maps; bias: q/k/v projection biases; sink: a learned logit per head in
     // the softmax denominator only; gate: sigmoid output gate per channel or per head; kv_from >= 0: keys and values of that layer's cache
+    // qk_norm = 2: one RMS norm over the whole q (and k) projection, before the split into heads, with a weight of that size.  softcap > 0:
+    // score <- softcap tanh(score / softcap).  slope_exp > 0: head h's score loses 2^(-slope_exp (h + 1) / heads) per position of distance.
+    // q_temp_every > 0: q at position p is multiplied by 1 + q_temp_coef ln(floor((p + 1) / q_temp_every) + 1).  out_bias: bias of the output projection
     int maps = 1, window = 0, keep_first = 0, qk_norm = 0, bias = 0, sink = 0, gate = HY_GATE_NONE, kv_from = -1;
-    float diff = 0.f;
+    float diff = 0.f, softcap = 0.f, slope_exp = 0.f, q_temp_coef = 0.f; int q_temp_every = 0, out_bias = 0;
+    HyLinear lin;                         // HY_LINEAR_ATTENTION, and the memory side of HY_ATTENTION_BESIDE_MEMORY (whose attention side uses the fields above)
     HyMoe moe;
 };
 
@@ -56,6 +79,7 @@ struct HybridConfig {
     int norm = HY_LAYER_NORM;             // the layers' (and the final) norm
     bool two_norms = false;               // mixer and feed-forward each read their own norm of the same residual
     float embed_scale = 1.f, logit_softcap = 0.f;      // x = embed[token] * scale; logits <- cap * tanh(logits / cap) (0: none)
+    bool post_norm = false; float post_alpha = 1.f;    // norm after the sum: x <- norm1(alpha x + mixer(x)), x <- norm2(alpha x + ff(x)); the sublayers read x itself
     std::vector<HyLayer> layers;
     int loop_start = 0, loop_stop = 0, loop_times = 0;    // times == 0: no looped block
     std::vector<HyRun> runs;
@@ -89,6 +113,7 @@ struct HybridConfig {
     static std::string registry_key(const std::string& architecture) {
         if (architecture == "Ratasun") return "ratasun";
         if (architecture == "Zurevik") return "zurevik";
+        if (architecture == "Rofizen") return "rofizen";
         return "";
     }
 
@@ -98,8 +123,9 @@ struct HybridConfig {
         HybridConfig c; c.dir = dir;
         c.arch = registry_key(j.str("architecture"));
         if (c.arch.empty()) throw std::runtime_error("config.json: unknown architecture '" + j.str("architecture") + "'");
-        const bool zu = c.arch == "zurevik";
+        const bool zu = c.arch == "zurevik", ro = c.arch == "rofizen";
         if (zu) { c.norm = HY_RMS_NORM; c.two_norms = true; }
+        if (ro) { c.post_norm = true; c.post_alpha = (float)num(j, "postln_alpha", "the model"); }
         if (const Json* e = j.get("embedding")) if (e->t == Json::Obj && e->get("scale")) c.embed_scale = (float)num(*e, "scale", "embedding");
         if (j.get("logit_softcap") && j.get("logit_softcap")->t == Json::Num) c.logit_softcap = (float)num(j, "logit_softcap", "the model");
         c.width = integer(j, "width", "the model"); c.vocab = integer(j, "vocab", "the model");
@@ -147,20 +173,57 @@ struct HybridConfig {
                         throw std::runtime_error("config.json: kv_from must name a layer with keys and values of its own and of this layer's sizes");
                 }
                 if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.window < 1 || l.keep_first < 0 || l.vdim > 256 || l.dim > 1024) throw std::runtime_error("config.json: bad attention sizes");
+            } else if (ro && (type == "gla" || type == "retention")) {
+                l.type = HY_LINEAR_ATTENTION; HyLinear& n = l.lin;
+                n.heads = l.heads = integer(m, "heads", type.c_str()); n.dim = l.dim = integer(m, "dim", type.c_str()); n.vdim = l.vdim = integer(m, "vdim", type.c_str());
+                if (type == "gla") { n.kind = HY_LIN_CHANNEL_DECAY; n.tau = (float)num(m, "tau", "gla"); n.norm = HY_LIN_NORM_HEAD_WEIGHT; if (!(n.tau > 0.f)) throw std::runtime_error("config.json: gla needs tau > 0"); }
+                else {
+                    n.kind = HY_LIN_HEAD_DECAY; n.norm = HY_LIN_NORM_NONE; n.q_scaled = false; n.k_scaled = true;
+                    const Json* d = m.get("decay");
+                    if (!d || d->t != Json::Arr || (int)d->a.size() != n.heads) throw std::runtime_error("config.json: retention needs a list 'decay' with one number per head");
+                    for (const Json& x : d->a) { if (x.t != Json::Num) throw std::runtime_error("config.json: 'decay' holds numbers"); n.decay.push_back((float)x.n); }
+                    const Json& r = obj(m, "rot", "retention");
+                    n.rot_base = (float)num(r, "base", "rot"); n.rot_dims = integer(r, "dims", "rot");
+                    if (n.rot_dims < 0 || n.rot_dims > n.dim || (n.rot_dims & 1)) throw std::runtime_error("config.json: rot.dims must be even and <= dim");
+                }
+                if (n.dim <= 0 || n.dim > 1024) throw std::runtime_error("config.json: bad linear-attention sizes");
+            } else if (ro && type == "parallel") {
+                // causal attention (left) beside a matrix memory (right), both reading the layer's input; the halves of their RMS-normed outputs are added
+                l.type = HY_ATTENTION_BESIDE_MEMORY;
+                const Json& a = obj(m, "left", "parallel"); const Json& b = obj(m, "right", "parallel");
+                l.heads = integer(a, "heads", "left"); l.kv_heads = integer(a, "kv_heads", "left"); l.dim = integer(a, "dim", "left"); l.vdim = integer(a, "vdim", "left");
+                l.scale = (float)num(a, "scale", "left"); l.softcap = (float)num(a, "softcap", "left"); l.slope_exp = 8.f;
+                const Json& qt = obj(a, "q_temp", "left");
+                l.q_temp_coef = (float)num(qt, "coef", "q_temp"); l.q_temp_every = integer(qt, "every", "q_temp");
+                l.window = 1 << 30; l.qk_norm = 2; l.bias = 1; l.out_bias = 1;
+                if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.vdim > 256 || l.dim > 1024 || l.q_temp_every < 1 || !(l.softcap > 0.f)) throw std::runtime_error("config.json: bad attention sizes");
+                HyLinear& n = l.lin;
+                n.kind = HY_LIN_MATRIX_MEMORY; n.heads = integer(b, "heads", "right"); n.dim = integer(b, "dim", "right"); n.vdim = integer(b, "vdim", "right");
+                n.gate_cap = (float)num(b, "gate_cap", "right"); n.norm = HY_LIN_NORM_ALL_WEIGHT; n.gate_silu = 0;
+                if (n.heads <= 0 || n.dim <= 0 || n.dim > 1024 || n.vdim <= 0 || !(n.gate_cap > 0.f)) throw std::runtime_error("config.json: bad matrix-memory sizes");
             } else throw std::runtime_error("config.json: unknown layer type '" + type + "'");
             const bool recurrent = l.type == HY_CHANNEL_DELTA || l.type == HY_MAMBA2;
             if (l.heads <= 0 || l.vdim <= 0 || (recurrent && (l.conv < 1 || l.conv > 16))) throw std::runtime_error("config.json: bad mixer sizes");
             const Json* mj = lj.get("mlp");
-            if (mj && mj->t == Json::Obj) {
+            if (mj && mj->t == Json::Obj && ro && mj->str("kind") == "dense") {
+                l.moe.present = true; l.moe.dense = true; l.moe.act = HY_EXPERT_RELU2; l.moe.experts = 1; l.moe.top = 1;
+                l.moe.ff = integer(*mj, "ff", "mlp");
+                if (l.moe.ff <= 0) throw std::runtime_error("config.json: bad feed-forward width");
+            } else if (mj && mj->t == Json::Obj) {
                 if (mj->str("kind") != "moe") throw std::runtime_error("config.json: unknown mlp kind '" + mj->str("kind") + "'");
                 const Json& r = obj(*mj, "router", "mlp");
                 l.moe.present = true; l.moe.ff = integer(obj(*mj, "expert", "mlp"), "ff", "expert");
                 l.moe.experts = integer(r, "experts", "router"); l.moe.top = integer(r, "top", "router");
                 if (zu) { l.moe.router = HY_ROUTER_SOFTMAX_CHOSEN; l.moe.act = HY_EXPERT_RELU2; }
+                else if (ro) {
+                    l.moe.router = HY_ROUTER_TOKEN_TABLE;
+                    if (const Json* sh = mj->get("shared")) if (sh->t == Json::Obj) { l.moe.shared_ff = integer(*sh, "ff", "shared"); if (l.moe.shared_ff <= 0) throw std::runtime_error("config.json: bad shared expert width"); }
+                    if (l.moe.ff <= 0) throw std::runtime_error("config.json: bad expert width");
+                }
                 else l.moe.scale = (float)num(r, "scale", "router");
                 if (const Json* g = r.get("groups")) if (g->t == Json::Obj) { l.moe.groups = integer(*g, "count", "groups"); l.moe.keep = integer(*g, "keep", "groups"); }
                 if (l.moe.groups <= 0 || l.moe.experts % l.moe.groups || l.moe.keep <= 0 || l.moe.keep > l.moe.groups || l.moe.top <= 0 ||
-                    l.moe.top > l.moe.keep * (l.moe.experts / l.moe.groups) || l.moe.top > 32 || l.moe.experts > 1024)
+                    l.moe.top > l.moe.keep * (l.moe.experts / l.moe.groups) || l.moe.top > 31 + (l.moe.shared_ff ? 0 : 1) || l.moe.experts > 1024)
                     throw std::runtime_error("config.json: bad router sizes");
             }
             c.layers.push_back(l);
@@ -179,6 +242,7 @@ struct HybridConfig {
                 if (r.cache_idx < 0 || (c.loop_times > 0 && layer >= c.loop_start && layer < c.loop_stop) || (c.loop_times > 0 && l.kv_from >= c.loop_start && l.kv_from < c.loop_stop))
                     throw std::runtime_error("config.json: a layer that reads another layer's cache cannot be part of a looped block");
             } else if (l.type == HY_LATENT_ATTENTION || l.type == HY_WINDOW_ATTENTION) { r.cache_idx = c.n_caches++; r.cache_owner = true; }
+            else if (l.type == HY_ATTENTION_BESIDE_MEMORY) { r.cache_idx = c.n_caches++; r.cache_owner = true; r.state_idx = c.n_states++; }     // a cache for the attention side, a state for the memory side
             else r.state_idx = c.n_states++;
             c.runs.push_back(r);
         };

@@ -20,7 +20,7 @@ using namespace hyk;
 // ---------------------------------------------------------------------------------------------------------------------------------
 template <typename TA, int MODE>
 __global__ void __launch_bounds__(256) hy_gemm_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ B, int ldb, void* Cv, int ldc, int M, int N, int K,
-                                                      const float* __restrict__ bias, float alpha, long long sA, long long sB, long long sC) {
+                                                      const float* __restrict__ bias, float alpha, long long sA, long long sB, long long sC, int act) {
     HY_PDL();
     __shared__ float As[16][64 + 4], Bs[16][64 + 4];
     A += (long long)blockIdx.z * sA; B += (long long)blockIdx.z * sB;
@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(256) hy_gemm_kernel(const TA* __restrict__ A, 
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             float v = acc[i][j] * alpha + (bias ? bias[n] : 0.f);
+            if (act == 1) { v = fmaxf(v, 0.f); v *= v; }
             const long long at = (long long)blockIdx.z * sC + (long long)m * ldc + n;
             if (MODE == HY_STORE) stf(reinterpret_cast<TA*>(Cv) + at, v);
             else if (MODE == HY_STORE_F32) reinterpret_cast<float*>(Cv)[at] = v;
@@ -64,10 +65,14 @@ __global__ void __launch_bounds__(256) hy_gemm_kernel(const TA* __restrict__ A, 
 }
 
 template <typename TA>
-__global__ void hy_embed_kernel(const int32_t* ids, const TA* table, float* x, float* x0, int T, int W, int vocab, float scale) {
+__global__ void hy_embed_kernel(const int32_t* ids, const TA* table, float* x, float* x0, int T, int W, int vocab, float scale, TA* h, int ldh) {
     HY_PDL();
     const int t = blockIdx.x; int id = ids[t]; id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float v = ldf(table + (long long)id * W + c) * scale; x[(long long)t * W + c] = v; if (x0) x0[(long long)t * W + c] = v; }
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = ldf(table + (long long)id * W + c) * scale; x[(long long)t * W + c] = v;
+        if (x0) x0[(long long)t * W + c] = v;
+        if (h) stf(h + (long long)t * ldh + c, v);
+    }
 }
 template <typename TA>
 __global__ void hy_concat_kernel(const float* x, const float* x0, TA* cat, int T, int W) {
@@ -618,40 +623,45 @@ __global__ void __launch_bounds__(128) hy_mamba_prep_kernel(HyMamba m, const TA*
 }
 
 constexpr int REC_COLS = 64;      // state columns (value channels) per CTA; a column evolves independently of the others
-template <bool DELTA>
+template <int MODE>
 __global__ void __launch_bounds__(REC_COLS) hy_recurrence_kernel(const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out,
-                                                                 float* state, int H, int QH, int D, int VD, HyRows r) {
+                                                                 float* state, int H, int QH, int D, int VD, HyRows r, float* norm_state, float* norm_out) {
+    constexpr bool DELTA = MODE == HY_REC_DELTA, CH = MODE != HY_REC_SCALAR;
     HY_PDL();
     extern __shared__ float sm[];
     float* S = sm;                         // [D][REC_COLS]
     float* qs = S + D * REC_COLS; float* ks = qs + D; float* ds = ks + D;
     const int seq = blockIdx.x, h = blockIdx.y, col = blockIdx.z * REC_COLS + threadIdx.x, j = threadIdx.x;
-    const bool ok = col < VD;
+    const bool is_norm = norm_state && col == VD, ok = col < VD || is_norm;      // the normaliser: one more value channel whose value is 1
     const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq], qh = h / (H / QH);
-    float* st = state + ((long long)r.seq_state[seq] * H + h) * D * VD;
-    for (int d = 0; d < D; ++d) S[d * REC_COLS + j] = (ok && pos0 > 0) ? st[(long long)d * VD + col] : 0.f;
+    float* st = is_norm ? norm_state + ((long long)r.seq_state[seq] * H + h) * D : state + ((long long)r.seq_state[seq] * H + h) * D * VD + col;
+    const long long st_stride = is_norm ? 1 : VD;
+    for (int d = 0; d < D; ++d) S[d * REC_COLS + j] = (ok && pos0 > 0) ? st[d * st_stride] : 0.f;
     for (int i = 0; i < len; ++i) {
         const long long t = row0 + i;
         __syncthreads();
         for (int d = j; d < D; d += REC_COLS) {
             qs[d] = qq[(t * QH + qh) * D + d]; ks[d] = kk[(t * QH + qh) * D + d];
-            if (DELTA) ds[d] = dec[(t * H + h) * D + d];
+            if (CH) ds[d] = dec[(t * H + h) * D + d];
         }
         __syncthreads();
-        const float v = ok ? vv[(t * H + h) * VD + col] : 0.f;
+        const float v = is_norm ? 1.f : ok ? vv[(t * H + h) * VD + col] : 0.f;
         float o = 0.f;
         if (DELTA) {
             float dot = 0.f;
             for (int d = 0; d < D; ++d) { const float s = S[d * REC_COLS + j] * ds[d]; S[d * REC_COLS + j] = s; dot = fmaf(s, ks[d], dot); }
             const float u = beta[t * H + h] * (v - dot);
             for (int d = 0; d < D; ++d) { const float s = fmaf(ks[d], u, S[d * REC_COLS + j]); S[d * REC_COLS + j] = s; o = fmaf(s, qs[d], o); }
+        } else if (CH) {
+            for (int d = 0; d < D; ++d) { const float s = fmaf(ks[d], v, S[d * REC_COLS + j] * ds[d]); S[d * REC_COLS + j] = s; o = fmaf(s, qs[d], o); }
         } else {
             const float a = dec[t * H + h];
             for (int d = 0; d < D; ++d) { const float s = fmaf(ks[d], v, S[d * REC_COLS + j] * a); S[d * REC_COLS + j] = s; o = fmaf(s, qs[d], o); }
         }
-        if (ok) out[(t * H + h) * VD + col] = o;
+        if (is_norm) norm_out[t * H + h] = o;
+        else if (ok) out[(t * H + h) * VD + col] = o;
     }
-    if (ok) for (int d = 0; d < D; ++d) st[(long long)d * VD + col] = S[d * REC_COLS + j];
+    if (ok) for (int d = 0; d < D; ++d) st[d * st_stride] = S[d * REC_COLS + j];
 }
 
 // Register-resident variant for dim <= DM (dim and vdim multiples of 4): a state column (value channel) lives in the registers of LANES
@@ -663,10 +673,12 @@ __global__ void __launch_bounds__(REC_COLS) hy_recurrence_kernel(const float* qq
 // token — and are read from there as 16-byte broadcasts.  The dependent chains of a step are split over four accumulators.  128 / LANES
 // columns per CTA.  The order of every sum is fixed for a given LANES, and LANES is chosen from the sizes alone, never from the step.
 constexpr int REC_STAGES = 8, REC_CTA_COLS = 128;
-template <bool DELTA, int DM, int LANES>
+template <int MODE, int DM, int LANES>
 __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __restrict__ qq, const float* __restrict__ kk, const float* __restrict__ vv,
                                                                 const float* __restrict__ dec, const float* __restrict__ beta, float* __restrict__ out,
-                                                                float* __restrict__ state, int H, int QH, int D, int VD, HyRows r) {
+                                                                float* __restrict__ state, int H, int QH, int D, int VD, HyRows r, float* __restrict__ norm_state,
+                                                                float* __restrict__ norm_out) {
+    constexpr bool DELTA = MODE == HY_REC_DELTA, CH = MODE != HY_REC_SCALAR;
     HY_PDL();
     extern __shared__ __align__(16) float rec_ring[];
     constexpr int stride = 3 * DM + REC_CTA_COLS + 4;     // floats per stage: q[DM] k[DM] g[DM] v[128] scalar (padded to 16 bytes); pad rows: q = k = 0, decay 1
@@ -674,16 +686,17 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
     const int tid = threadIdx.x, part = tid / COLS, cl = tid % COLS, col = blockIdx.z * COLS + cl, r0 = part * DR;      // LANES = 4: part = warp
     __shared__ float rec_pd[LANES][COLS], rec_po[2][LANES][COLS];      // partial dot products of the current token; partial read-outs of this and the last token
     const int seq = blockIdx.x, h = blockIdx.y;
-    const bool ok = col < VD;
+    const bool is_norm = norm_state && col == VD, ok = col < VD || is_norm;      // the normaliser: one more value channel whose value is 1
     const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq], qh = h / (H / QH);
-    float* st = state + ((long long)r.seq_state[seq] * H + h) * D * VD;
+    float* st = is_norm ? norm_state + ((long long)r.seq_state[seq] * H + h) * D : state + ((long long)r.seq_state[seq] * H + h) * D * VD + col;
+    const long long st_stride = is_norm ? 1 : VD;
     float S[DR];
 #pragma unroll
-    for (int i = 0; i < DR; ++i) S[i] = (ok && pos0 > 0 && r0 + i < D) ? st[(long long)(r0 + i) * VD + col] : 0.f;
+    for (int i = 0; i < DR; ++i) S[i] = (ok && pos0 > 0 && r0 + i < D) ? st[(r0 + i) * st_stride] : 0.f;
     for (int i = tid; i < REC_STAGES * stride; i += 128) { const int w = i % stride; rec_ring[i] = (w >= 2 * DM && w < 3 * DM) ? 1.f : 0.f; }
     __syncthreads();
     // this thread's copy roles: one 16-byte piece per token (threads 0..95: q / k / decay rows, 96..127: the values), thread 0 also the scalar
-    const int dq = D / 4, n_vec = (DELTA ? 3 : 2) * dq;
+    const int dq = D / 4, n_vec = (CH ? 3 : 2) * dq;
     const float* src = nullptr; int dst = 0; long long step = 0;
     if (tid < n_vec) {
         const int which = tid / dq, c = tid - which * dq;
@@ -693,7 +706,7 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
         const int c = tid - 96;
         if (c * 4 < COLS && blockIdx.z * COLS + c * 4 < VD) { src = vv + ((long long)row0 * H + h) * VD + blockIdx.z * COLS + c * 4; step = (long long)H * VD; dst = 3 * DM + c * 4; }
     }
-    const float* src_sc = tid == 0 ? (DELTA ? beta : dec) + (long long)row0 * H + h : nullptr;
+    const float* src_sc = (tid == 0 && MODE != HY_REC_CHANNEL) ? (DELTA ? beta : dec) + (long long)row0 * H + h : nullptr;
     int issued = 0;
     auto issue = [&]() {                             // next token of the sequence's rows -> ring slot issued % REC_STAGES
         if (issued < len) {
@@ -705,9 +718,10 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     for (int i = 0; i < REC_STAGES - 1; ++i) issue();
-    float* op = out + ((long long)row0 * H + h) * VD + col;
+    float* op = is_norm ? norm_out + (long long)row0 * H + h : out + ((long long)row0 * H + h) * VD + col;
+    const long long o_stride = is_norm ? H : (long long)H * VD;
     auto join = [&](int i) {                         // LANES = 4: token i's read-out, its four partial sums added in warp order by warp i % 4
-        if (ok && part == (i & 3)) { const float* p = &rec_po[i & 1][0][cl]; op[(long long)i * H * VD] = (p[0] + p[COLS]) + (p[2 * COLS] + p[3 * COLS]); }
+        if (ok && part == (i & 3)) { const float* p = &rec_po[i & 1][0][cl]; op[i * o_stride] = (p[0] + p[COLS]) + (p[2 * COLS] + p[3 * COLS]); }
     };
     for (int i = 0; i < len; ++i) {
         asm volatile("cp.async.wait_group %0;" ::"n"(REC_STAGES - 2) : "memory");
@@ -715,7 +729,7 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
         issue();
         if (LANES == 4 && i > 0) join(i - 1);        // its partials were written before this barrier; their buffer is written again at token i + 1, behind the next one
         const float* slot = rec_ring + (i % REC_STAGES) * stride;
-        const float v = slot[3 * DM + cl], sc = slot[3 * DM + REC_CTA_COLS];
+        const float v = is_norm ? 1.f : slot[3 * DM + cl], sc = slot[3 * DM + REC_CTA_COLS];
         const float* sq = slot + r0; const float* sk = slot + DM + r0; const float* sg = slot + 2 * DM + r0;
         float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
         if (DELTA) {
@@ -739,6 +753,13 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
                 S[j] = fmaf(k4.x, u, S[j]); S[j + 1] = fmaf(k4.y, u, S[j + 1]); S[j + 2] = fmaf(k4.z, u, S[j + 2]); S[j + 3] = fmaf(k4.w, u, S[j + 3]);
                 o0 = fmaf(S[j], q4.x, o0); o1 = fmaf(S[j + 1], q4.y, o1); o2 = fmaf(S[j + 2], q4.z, o2); o3 = fmaf(S[j + 3], q4.w, o3);
             }
+        } else if (CH) {
+#pragma unroll
+            for (int j = 0; j < DR; j += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(sq + j), k4 = *reinterpret_cast<const float4*>(sk + j), g4 = *reinterpret_cast<const float4*>(sg + j);
+                S[j] = fmaf(k4.x, v, S[j] * g4.x); S[j + 1] = fmaf(k4.y, v, S[j + 1] * g4.y); S[j + 2] = fmaf(k4.z, v, S[j + 2] * g4.z); S[j + 3] = fmaf(k4.w, v, S[j + 3] * g4.w);
+                o0 = fmaf(S[j], q4.x, o0); o1 = fmaf(S[j + 1], q4.y, o1); o2 = fmaf(S[j + 2], q4.z, o2); o3 = fmaf(S[j + 3], q4.w, o3);
+            }
         } else {
 #pragma unroll
             for (int j = 0; j < DR; j += 4) {
@@ -749,24 +770,26 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
         }
         float o = (o0 + o1) + (o2 + o3);
         if (LANES == 4) rec_po[i & 1][part][cl] = o;
-        else if (ok) op[(long long)i * H * VD] = o;
+        else if (ok) op[i * o_stride] = o;
     }
     if (LANES == 4 && len > 0) { __syncthreads(); join(len - 1); }
     if (ok)
 #pragma unroll
-        for (int i = 0; i < DR; ++i) if (r0 + i < D) st[(long long)(r0 + i) * VD + col] = S[i];
+        for (int i = 0; i < DR; ++i) if (r0 + i < D) st[(r0 + i) * st_stride] = S[i];
 }
 
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_gated_norm_kernel(const float* o, int C, int group, const float* w, int wlen, const TA* gate, int ld_gate, int gate_before, int act,
-                                                             const float* skip, int skip_block, const TA* xs, int ld_xs, TA* out, int ld_out, float eps) {
+                                                             const float* skip, int skip_block, const TA* xs, int ld_xs, TA* out, int ld_out, float eps,
+                                                             const float* den_dot, const float* den_floor) {
     HY_PDL();
     __shared__ float red[32];
     const int t = blockIdx.x, c0 = blockIdx.y * group;
+    const float dv = den_dot ? 1.0f / (fmaxf(fabsf(den_dot[(long long)t * gridDim.y + blockIdx.y]), den_floor[(long long)t * gridDim.y + blockIdx.y]) + 1e-6f) : 1.f;
     float ss = 0.f;
     for (int i = threadIdx.x; i < group; i += blockDim.x) {
         const int c = c0 + i;
-        float v = o[(long long)t * C + c];
+        float v = o[(long long)t * C + c] * dv;
         if (skip) v = fmaf(skip[c / skip_block], ldf(xs + (long long)t * ld_xs + c), v);
         if (gate_before) { const float g = ldf(gate + (long long)t * ld_gate + c); v *= act ? siluf_(g) : sigmoidf_(g); }
         ss += v * v;
@@ -774,11 +797,11 @@ __global__ void __launch_bounds__(128) hy_gated_norm_kernel(const float* o, int 
     const float rr = 1.0f / sqrtf(block_sum(ss, red) / (float)group + eps);
     for (int i = threadIdx.x; i < group; i += blockDim.x) {
         const int c = c0 + i;
-        float v = o[(long long)t * C + c];
+        float v = o[(long long)t * C + c] * dv;
         if (skip) v = fmaf(skip[c / skip_block], ldf(xs + (long long)t * ld_xs + c), v);
         const float g = ldf(gate + (long long)t * ld_gate + c), ga = act ? siluf_(g) : sigmoidf_(g);
         if (gate_before) v *= ga;
-        v = v * rr * w[c % wlen];
+        v = v * rr * (w ? w[c % wlen] : 1.f);
         if (!gate_before) v *= ga;
         stf(out + (long long)t * ld_out + c, v);
     }
@@ -799,15 +822,19 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, const float* f) {
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_gated_norm_warp_kernel(const float* __restrict__ o, int C, int group, const float* __restrict__ w, int wlen, const TA* __restrict__ gate,
                                                                   int ld_gate, int gate_before, int act, const float* __restrict__ skip, int skip_block, const TA* __restrict__ xs,
-                                                                  int ld_xs, TA* __restrict__ out, int ld_out, float eps, long long n_items) {
+                                                                  int ld_xs, TA* __restrict__ out, int ld_out, float eps, long long n_items,
+                                                                  const float* __restrict__ den_dot, const float* __restrict__ den_floor) {
     HY_PDL();
     const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (item >= n_items) return;
     const int lane = threadIdx.x & 31, G = C / group, t = (int)(item / G), c0 = (int)(item % G) * group;
+    const float dv = den_dot ? 1.0f / (fmaxf(fabsf(den_dot[item]), den_floor[item]) + 1e-6f) : 1.f;
     float ss = 0.f, v[4], g[4], x4[4];
     for (int i = lane * 4; i < group; i += 128) {
         const int c = c0 + i;
         ld4(o + (long long)t * C + c, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] *= dv;
         if (skip) { ld4(xs + (long long)t * ld_xs + c, x4);
 #pragma unroll
             for (int e = 0; e < 4; ++e) v[e] = fmaf(skip[(c + e) / skip_block], x4[e], v[e]); }
@@ -821,6 +848,8 @@ __global__ void __launch_bounds__(128) hy_gated_norm_warp_kernel(const float* __
     for (int i = lane * 4; i < group; i += 128) {
         const int c = c0 + i;
         ld4(o + (long long)t * C + c, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] *= dv;
         if (skip) { ld4(xs + (long long)t * ld_xs + c, x4);
 #pragma unroll
             for (int e = 0; e < 4; ++e) v[e] = fmaf(skip[(c + e) / skip_block], x4[e], v[e]); }
@@ -829,7 +858,7 @@ __global__ void __launch_bounds__(128) hy_gated_norm_warp_kernel(const float* __
         for (int e = 0; e < 4; ++e) {
             const float ga = act ? siluf_(g[e]) : sigmoidf_(g[e]);
             if (gate_before) v[e] *= ga;
-            v[e] = v[e] * rr * w[(c + e) % wlen];
+            v[e] = v[e] * rr * (w ? w[(c + e) % wlen] : 1.f);
             if (!gate_before) v[e] *= ga;
         }
         st4(out + (long long)t * ld_out + c, v);
@@ -950,7 +979,7 @@ __global__ void __launch_bounds__(256) hy_moe_up_relu2_kernel(const TA* h, int l
     if (lane == 0) stf(act + (long long)row * ffp + f, v);
 }
 template <typename TA>
-__global__ void __launch_bounds__(256) hy_moe_down_kernel(const TA* act, const TA* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x) {
+__global__ void __launch_bounds__(256) hy_moe_down_kernel(const TA* act, const TA* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x, float beta) {
     HY_PDL();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = blockIdx.y * 8 + warp;
     if (n >= W) return;
@@ -963,7 +992,7 @@ __global__ void __launch_bounds__(256) hy_moe_down_kernel(const TA* act, const T
         d = warp_sum(d);
         acc = fmaf(wgt[(long long)t * top + c], d, acc);
     }
-    if (lane == 0) x[(long long)t * W + n] += acc;
+    if (lane == 0) x[(long long)t * W + n] = fmaf(beta, x[(long long)t * W + n], acc);
 }
 
 // Expert plan in three small kernels: (1) pairs per expert, (2) one CTA lays the experts' 128-row tiles out one after the other, (3) every
@@ -1039,7 +1068,7 @@ __global__ void hy_moe_gather_kernel(const __nv_bfloat16* h, int ldh, int W, con
     for (int c = threadIdx.x * 8; c < W; c += blockDim.x * 8)
         *reinterpret_cast<uint4*>(out + (long long)row * W + c) = src >= 0 ? *reinterpret_cast<const uint4*>(h + (long long)(src / top) * ldh + c) : z;
 }
-__global__ void hy_moe_combine_kernel(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W) {
+__global__ void hy_moe_combine_kernel(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W, float beta) {
     HY_PDL();
     const int t = blockIdx.x;                       // W and ldy are multiples of 4 on this path
     for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
@@ -1050,7 +1079,7 @@ __global__ void hy_moe_combine_kernel(const float* y, int ldy, const int32_t* ds
             acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
         }
         float4* xp = reinterpret_cast<float4*>(x + (long long)t * W + c);
-        float4 xv = *xp; xv.x += acc.x; xv.y += acc.y; xv.z += acc.z; xv.w += acc.w; *xp = xv;
+        float4 xv = *xp; xv.x = fmaf(beta, xv.x, acc.x); xv.y = fmaf(beta, xv.y, acc.y); xv.z = fmaf(beta, xv.z, acc.z); xv.w = fmaf(beta, xv.w, acc.w); *xp = xv;
     }
 }
 
@@ -1089,25 +1118,25 @@ using bf = __nv_bfloat16;
 
 template <typename TA>
 static cudaError_t gemm_t(int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias, float alpha, int batch,
-                          long long sA, long long sB, long long sC, cudaStream_t s) {
+                          long long sA, long long sB, long long sC, cudaStream_t s, int act) {
     dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
     const TA* a = reinterpret_cast<const TA*>(A); const TA* b = reinterpret_cast<const TA*>(B);
     switch (mode) {
-        case HY_STORE: return launch_plain(hy_gemm_kernel<TA, HY_STORE>, grid, dim3(256), 0, s, a, lda, b, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC);
-        case HY_STORE_F32: return launch_plain(hy_gemm_kernel<TA, HY_STORE_F32>, grid, dim3(256), 0, s, a, lda, b, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC);
-        case HY_ACC_F32: return launch_plain(hy_gemm_kernel<TA, HY_ACC_F32>, grid, dim3(256), 0, s, a, lda, b, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC);
+        case HY_STORE: return launch_plain(hy_gemm_kernel<TA, HY_STORE>, grid, dim3(256), 0, s, a, lda, b, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC, act);
+        case HY_STORE_F32: return launch_plain(hy_gemm_kernel<TA, HY_STORE_F32>, grid, dim3(256), 0, s, a, lda, b, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC, act);
+        case HY_ACC_F32: return launch_plain(hy_gemm_kernel<TA, HY_ACC_F32>, grid, dim3(256), 0, s, a, lda, b, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC, act);
     }
     return cudaErrorInvalidValue;
 }
 cudaError_t hy_gemm(bool f32, int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias, float alpha, int batch,
-                    long long sA, long long sB, long long sC, cudaStream_t s) {
+                    long long sA, long long sB, long long sC, cudaStream_t s, int act) {
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return cudaSuccess;
-    return f32 ? gemm_t<float>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s)
-               : gemm_t<bf>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s);
+    return f32 ? gemm_t<float>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s, act)
+               : gemm_t<bf>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s, act);
 }
-cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, float scale, cudaStream_t s) {
-    return f32 ? launch_plain(hy_embed_kernel<float>, dim3(T), dim3(128), 0, s, ids, (const float*)table, x, x0, T, W, vocab, scale)
-               : launch_plain(hy_embed_kernel<bf>, dim3(T), dim3(128), 0, s, ids, (const bf*)table, x, x0, T, W, vocab, scale);
+cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, float scale, cudaStream_t s, void* h, int ldh) {
+    return f32 ? launch_plain(hy_embed_kernel<float>, dim3(T), dim3(128), 0, s, ids, (const float*)table, x, x0, T, W, vocab, scale, (float*)h, ldh)
+               : launch_plain(hy_embed_kernel<bf>, dim3(T), dim3(128), 0, s, ids, (const bf*)table, x, x0, T, W, vocab, scale, (bf*)h, ldh);
 }
 cudaError_t hy_concat(bool f32, const float* x, const float* x0, void* cat, int T, int W, cudaStream_t s) {
     return f32 ? launch_plain(hy_concat_kernel<float>, dim3(T), dim3(128), 0, s, x, x0, (float*)cat, T, W)
@@ -1229,47 +1258,53 @@ cudaError_t hy_mamba_prep(bool f32, const HyMamba& m, const void* conv, int ld_c
     return f32 ? launch_plain(hy_mamba_prep_kernel<float>, dim3(T), dim3(128), 0, s, m, (const float*)conv, ld_conv, (const float*)dt, ld_dt, A_log, dt_bias, qq, kk, vv, dec)
                : launch_plain(hy_mamba_prep_kernel<bf>, dim3(T), dim3(128), 0, s, m, (const bf*)conv, ld_conv, (const bf*)dt, ld_dt, A_log, dt_bias, qq, kk, vv, dec);
 }
-cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out, float* state, int heads,
-                          int qk_heads, int dim, int vdim, const HyRows& r, cudaStream_t s) {
+cudaError_t hy_recurrence(int mode, const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out, float* state, int heads,
+                          int qk_heads, int dim, int vdim, const HyRows& r, cudaStream_t s, float* norm_state, float* norm_out) {
+    if (mode < 0 || mode > 2 || (norm_state && (mode == HY_REC_DELTA || !norm_out))) return cudaErrorInvalidValue;
+    const int cols = vdim + (norm_state ? 1 : 0);
     if (dim <= 128 && dim % 4 == 0 && vdim % 4 == 0) {
         // one thread per column runs a chain of 4 dim dependent-ish operations per token with one or two warps per scheduler; beyond 32
         // rows the rows are split over the CTA's four warps (by the sizes alone: the order of a sum never depends on the step)
         const bool wide = dim > 32;
-        dim3 grid(r.S, heads, (vdim * (wide ? 4 : 1) + REC_CTA_COLS - 1) / REC_CTA_COLS);
+        dim3 grid(r.S, heads, (cols * (wide ? 4 : 1) + REC_CTA_COLS - 1) / REC_CTA_COLS);
         const int dm = dim <= 32 ? 32 : dim <= 64 ? 64 : 128;
         const size_t ring = (size_t)REC_STAGES * (3 * dm + REC_CTA_COLS + 4) * 4;
-#define HY_REC(DL, DM, LN) launch_plain(hy_recurrence_reg_kernel<DL, DM, LN>, grid, dim3(128), ring, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r)
-#define HY_REC_DM(DL, LN) (dm == 32 ? HY_REC(DL, 32, LN) : dm == 64 ? HY_REC(DL, 64, LN) : HY_REC(DL, 128, LN))
-        if (delta) return wide ? HY_REC_DM(true, 4) : HY_REC_DM(true, 1);
-        return wide ? HY_REC_DM(false, 4) : HY_REC_DM(false, 1);
+#define HY_REC(MD, DM, LN) launch_plain(hy_recurrence_reg_kernel<MD, DM, LN>, grid, dim3(128), ring, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r, norm_state, norm_out)
+#define HY_REC_DM(MD, LN) (dm == 32 ? HY_REC(MD, 32, LN) : dm == 64 ? HY_REC(MD, 64, LN) : HY_REC(MD, 128, LN))
+        if (mode == HY_REC_DELTA) return wide ? HY_REC_DM(HY_REC_DELTA, 4) : HY_REC_DM(HY_REC_DELTA, 1);
+        if (mode == HY_REC_CHANNEL) return wide ? HY_REC_DM(HY_REC_CHANNEL, 4) : HY_REC_DM(HY_REC_CHANNEL, 1);
+        return wide ? HY_REC_DM(HY_REC_SCALAR, 4) : HY_REC_DM(HY_REC_SCALAR, 1);
 #undef HY_REC_DM
 #undef HY_REC
     }
     const size_t smem = (size_t)(dim * REC_COLS + 3 * dim) * 4;
-    dim3 grid(r.S, heads, (vdim + REC_COLS - 1) / REC_COLS);
-    static bool attr_done[2][16] = {};
+    dim3 grid(r.S, heads, (cols + REC_COLS - 1) / REC_COLS);
+    static bool attr_done[3][16] = {};
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    if (smem > 48 * 1024) {
-        cudaError_t e = delta ? ensure_dynamic_smem(hy_recurrence_kernel<true>, 200 * 1024, attr_done[0]) : ensure_dynamic_smem(hy_recurrence_kernel<false>, 200 * 1024, attr_done[1]);      // the limit is set once per kernel and device: raise it to the most any size may ask for
+    if (smem > 48 * 1024) {      // the limit is set once per kernel and device: raise it to the most any size may ask for
+        cudaError_t e = mode == HY_REC_DELTA ? ensure_dynamic_smem(hy_recurrence_kernel<HY_REC_DELTA>, 200 * 1024, attr_done[0])
+                      : mode == HY_REC_CHANNEL ? ensure_dynamic_smem(hy_recurrence_kernel<HY_REC_CHANNEL>, 200 * 1024, attr_done[2])
+                                               : ensure_dynamic_smem(hy_recurrence_kernel<HY_REC_SCALAR>, 200 * 1024, attr_done[1]);
         if (e != cudaSuccess) return e;
     }
-    return delta ? launch_plain(hy_recurrence_kernel<true>, grid, dim3(REC_COLS), smem, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r)
-                 : launch_plain(hy_recurrence_kernel<false>, grid, dim3(REC_COLS), smem, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r);
+#define HY_RECG(MD) launch_plain(hy_recurrence_kernel<MD>, grid, dim3(REC_COLS), smem, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r, norm_state, norm_out)
+    return mode == HY_REC_DELTA ? HY_RECG(HY_REC_DELTA) : mode == HY_REC_CHANNEL ? HY_RECG(HY_REC_CHANNEL) : HY_RECG(HY_REC_SCALAR);
+#undef HY_RECG
 }
 cudaError_t hy_gated_norm(bool f32, const float* o, int C, int group, const float* w, int wlen, const void* gate, int ld_gate, int gate_before, int act, const float* skip,
-                          int skip_block, const void* xs, int ld_xs, void* out, int ld_out, float eps, int T, cudaStream_t s) {
+                          int skip_block, const void* xs, int ld_xs, void* out, int ld_out, float eps, int T, cudaStream_t s, const float* den_dot, const float* den_floor) {
     // The choice of kernel rests on the sizes of the model only, never on the step: a row's bits do not depend on its batch.
     const size_t ea = f32 ? 4 : 2;
     auto al = [](const void* p, size_t a) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
     if (group % 4 == 0 && group <= 512 && C % 4 == 0 && ld_gate % 4 == 0 && ld_out % 4 == 0 && (!skip || ld_xs % 4 == 0) && al(o, 16) && al(gate, 4 * ea) && al(out, 4 * ea) && al(xs, 4 * ea)) {
         const long long n = (long long)T * (C / group);
         const dim3 g((unsigned)((n + 3) / 4));
-        return f32 ? launch_plain(hy_gated_norm_warp_kernel<float>, g, dim3(128), 0, s, o, C, group, w, wlen, (const float*)gate, ld_gate, gate_before, act, skip, skip_block, (const float*)xs, ld_xs, (float*)out, ld_out, eps, n)
-                   : launch_plain(hy_gated_norm_warp_kernel<bf>, g, dim3(128), 0, s, o, C, group, w, wlen, (const bf*)gate, ld_gate, gate_before, act, skip, skip_block, (const bf*)xs, ld_xs, (bf*)out, ld_out, eps, n);
+        return f32 ? launch_plain(hy_gated_norm_warp_kernel<float>, g, dim3(128), 0, s, o, C, group, w, wlen, (const float*)gate, ld_gate, gate_before, act, skip, skip_block, (const float*)xs, ld_xs, (float*)out, ld_out, eps, n, den_dot, den_floor)
+                   : launch_plain(hy_gated_norm_warp_kernel<bf>, g, dim3(128), 0, s, o, C, group, w, wlen, (const bf*)gate, ld_gate, gate_before, act, skip, skip_block, (const bf*)xs, ld_xs, (bf*)out, ld_out, eps, n, den_dot, den_floor);
     }
     dim3 grid(T, C / group);
-    return f32 ? launch_plain(hy_gated_norm_kernel<float>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const float*)gate, ld_gate, gate_before, act, skip, skip_block, (const float*)xs, ld_xs, (float*)out, ld_out, eps)
-               : launch_plain(hy_gated_norm_kernel<bf>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const bf*)gate, ld_gate, gate_before, act, skip, skip_block, (const bf*)xs, ld_xs, (bf*)out, ld_out, eps);
+    return f32 ? launch_plain(hy_gated_norm_kernel<float>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const float*)gate, ld_gate, gate_before, act, skip, skip_block, (const float*)xs, ld_xs, (float*)out, ld_out, eps, den_dot, den_floor)
+               : launch_plain(hy_gated_norm_kernel<bf>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const bf*)gate, ld_gate, gate_before, act, skip, skip_block, (const bf*)xs, ld_xs, (bf*)out, ld_out, eps, den_dot, den_floor);
 }
 cudaError_t hy_moe_router(const HyRouter& m, const float* logits, int ldz, const float* correction, int32_t* idx, float* wgt, int T, cudaStream_t s) {
     const size_t smem = (size_t)4 * (2 * m.experts + m.groups) * 4;
@@ -1287,10 +1322,10 @@ cudaError_t hy_moe_gate_up(bool f32, int relu2, const void* h, int ldh, const vo
     return f32 ? launch_plain(hy_moe_gate_up_kernel<float>, grid, dim3(256), 0, s, (const float*)h, ldh, (const float*)gu, ldw, W, ff, ffp, idx, top, (float*)act)
                : launch_plain(hy_moe_gate_up_kernel<bf>, grid, dim3(256), 0, s, (const bf*)h, ldh, (const bf*)gu, ldw, W, ff, ffp, idx, top, (bf*)act);
 }
-cudaError_t hy_moe_down(bool f32, const void* act, const void* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x, int T, cudaStream_t s) {
+cudaError_t hy_moe_down(bool f32, const void* act, const void* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x, int T, cudaStream_t s, float beta) {
     dim3 grid(T, (W + 7) / 8);
-    return f32 ? launch_plain(hy_moe_down_kernel<float>, grid, dim3(256), 0, s, (const float*)act, (const float*)down, W, ffp, idx, wgt, top, x)
-               : launch_plain(hy_moe_down_kernel<bf>, grid, dim3(256), 0, s, (const bf*)act, (const bf*)down, W, ffp, idx, wgt, top, x);
+    return f32 ? launch_plain(hy_moe_down_kernel<float>, grid, dim3(256), 0, s, (const float*)act, (const float*)down, W, ffp, idx, wgt, top, x, beta)
+               : launch_plain(hy_moe_down_kernel<bf>, grid, dim3(256), 0, s, (const bf*)act, (const bf*)down, W, ffp, idx, wgt, top, x, beta);
 }
 cudaError_t hy_moe_plan(const int32_t* idx, int T, int top, int experts, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out, int32_t* dst_of, int max_tiles,
                         cudaStream_t s) {
@@ -1307,8 +1342,8 @@ cudaError_t hy_moe_plan(const int32_t* idx, int T, int top, int experts, int32_t
 cudaError_t hy_moe_gather(const void* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, void* out, int max_tiles, cudaStream_t s) {
     return launch_plain(hy_moe_gather_kernel, dim3(max_tiles * 128), dim3(128), 0, s, (const bf*)h, ldh, W, row_src, n_tiles, top, (bf*)out);
 }
-cudaError_t hy_moe_combine(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W, int T, cudaStream_t s) {
-    return launch_plain(hy_moe_combine_kernel, dim3(T), dim3(256), 0, s, y, ldy, dst_of, wgt, top, x, W);
+cudaError_t hy_moe_combine(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W, int T, cudaStream_t s, float beta) {
+    return launch_plain(hy_moe_combine_kernel, dim3(T), dim3(256), 0, s, y, ldy, dst_of, wgt, top, x, W, beta);
 }
 cudaError_t hy_gather_rows_f32(const float* x, const int32_t* rows, float* out, int n, int W, cudaStream_t s) {
     if (n <= 0) return cudaSuccess;

@@ -27,11 +27,13 @@ struct HyRows {
 enum HyGemmMode : int { HY_STORE = 0, HY_STORE_F32 = 1, HY_ACC_F32 = 2 };
 // C[z][M,N] (op)= alpha * A[z][M,K] . B[z][N,K]^T (+ bias[N]), z < batch with element strides sA/sB/sC.  Plain tiled FMA GEMM in fp32
 // accumulation for any sizes: the fp32 mode's matrix product, and the bf16 mode's fallback where a shape does not fit the tensor-core tiles.
+// act = 1: the stored value is relu(.)^2 (HY_STORE / HY_STORE_F32)
 cudaError_t hy_gemm(bool f32, int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias,
-                    float alpha, int batch, long long sA, long long sB, long long sC, cudaStream_t s);
+                    float alpha, int batch, long long sA, long long sB, long long sC, cudaStream_t s, int act = 0);
 
 // x[t] = table[ids[t]] * scale (fp32); x0 (optional) keeps a copy for a looped block's re-injection
-cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, float scale, cudaStream_t s);
+// h (optional, [T, ldh] in the activation type): the same rows as the input of sublayers that read the residual itself
+cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, float scale, cudaStream_t s, void* h = nullptr, int ldh = 0);
 // cat[t] = [x[t] ; x0[t]] in the activation type (input of the looped block's re-injection projection)
 cudaError_t hy_concat(bool f32, const float* x, const float* x0, void* cat, int T, int W, cudaStream_t s);
 // out[t] = (x[t] - mean) / sqrt(var + eps) * w   (optionally of the rows `rows[i]` only)
@@ -41,10 +43,20 @@ cudaError_t hy_layernorm(bool f32, const float* x, const int32_t* rows, const fl
 // mixer and feed-forward read separate norms of the same residual, or a single RMS norm
 cudaError_t hy_rmsnorm_pair(bool f32, const float* x, const int32_t* rows, const float* w1, void* out1, const float* w2, void* out2, int ldo, int T, int W, float eps, cudaStream_t s);
 
+// Norm after the sum, in place on the fp32 residual: v = beta x[t] + branch, x[t] <- layer norm of v with weight w (mean taken off, eps inside
+// the root), and h[t] (activation type) = the new x[t], the next sublayer's input.  branch: nothing (y1 == null: the sublayer has already added
+// itself into x), y1[t], or — when rw1 is given — branch_scale * (rms_norm(y1[t]) * rw1 + rms_norm(y2[t]) * rw2), two sublayers side by side
+// whose outputs are RMS-normed over the width before they meet.
+cudaError_t hy_post_norm(bool f32, float* x, float beta, const float* y1, const float* rw1, const float* y2, const float* rw2, float branch_scale, const float* w, void* h, int ldh,
+                         int T, int W, float eps, cudaStream_t s);
+
 // Windowed attention over cached keys and values.  A cache row holds one token: [kv_heads x maps x dim keys | kv_heads x vdim values].
 // Position i sees j <= i with i - j < window or j < keep_first.  maps = 2: differential attention, out = (a1 - lambda a2) / rms(.) * out_scale
 // per head.  gate: 0 none, 1 sigmoid(gate[t, head * vdim + c]), 2 sigmoid(gate[t, head]).  sink (per head, or null) joins the denominator only.
-struct HyWinAttn { int heads, kv_heads, dim, vdim, maps, window, keep_first, qk_norm, gate; float scale, lambda, out_scale; };
+// Score modifiers (all optional): softcap > 0: s <- softcap tanh(s / softcap) after the scale; slope_exp > 0: head h then loses
+// 2^(-slope_exp (h + 1) / heads) * (i - j).  qk_norm = 2: one RMS norm over the whole q (k) projection of a row, weights [heads maps dim]
+// ([kv_heads maps dim]); q_temp_every > 0: the query at position p is multiplied by 1 + q_temp_coef ln(floor((p + 1) / q_temp_every) + 1).
+struct HyWinAttn { int heads, kv_heads, dim, vdim, maps, window, keep_first, qk_norm, gate; float scale, lambda, out_scale; float softcap = 0.f, slope_exp = 0.f, q_temp_coef = 0.f; int q_temp_every = 0; };
 bool hy_win_supported(const HyWinAttn& a);
 // q [T, ldq] (head by head, map by map): RMS-normed in place with q_norm_w when qk_norm; k / v [T, ldkv] (null: this layer reads a cache
 // another layer fills): keys normed alike with k_norm_w, both stored at cache row slots[t]
@@ -121,12 +133,31 @@ cudaError_t hy_mamba_prep(bool f32, const HyMamba& m, const void* xbc_conv, int 
 //   delta:  S <- diag(dec_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
 //   plain:  S <- dec_t S + k_t v_t^T;                                            o_t = S^T q_t
 // qq/kk: [T, qk_heads, dim]; vv/out: [T, heads, vdim]; dec: [T, heads, dim] (delta) or [T, heads]; head h reads q/k head h / (heads / qk_heads)
-cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out,
-                          float* state, int heads, int qk_heads, int dim, int vdim, const HyRows& r, cudaStream_t s);
+// mode HY_REC_CHANNEL: S <- diag(dec_t) S + k_t v_t^T with dec [T, heads, dim] (gated linear attention).
+// norm_state != null (plain modes): one more value channel whose value is always 1 — the normaliser n_t = dec_t n_(t-1) + k_t, kept in
+// norm_state [slots, heads, dim]; its read-out n_t . q_t goes to norm_out [T, heads].
+enum HyRecMode : int { HY_REC_SCALAR = 0, HY_REC_DELTA = 1, HY_REC_CHANNEL = 2 };
+cudaError_t hy_recurrence(int mode, const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out,
+                          float* state, int heads, int qk_heads, int dim, int vdim, const HyRows& r, cudaStream_t s, float* norm_state = nullptr, float* norm_out = nullptr);
+
+// Operands of the linear-attention recurrences, all fp32.  q / k / v: projection outputs [T, ld] (head by head).
+struct HyLinPrep { int heads, dim, vdim; bool q_scaled, k_scaled; int rot_dims; };     // dim^-1/2 on q and / or on k (after the rotation); rotate-half rotary on the first rot_dims channels of every head of q and k (0: none): channel i pairs with i + rot_dims / 2, cos / sin tables [position, rot_dims / 2]
+// channel decay (z != null): dec[t, h, d] = sigmoid(z[t, h, d])^(1 / tau) = exp(logsigmoid(z) / tau), in place on the fp32 z (= dec);  head decay: dec[t, h] = decay[h]
+cudaError_t hy_lin_prep(bool f32, const HyLinPrep& p, const void* q, const void* k, const void* v, int ld, float* qq, float* kk, float* vv, float* dec_channel, float tau,
+                        const float* decay_head, float* dec_head, const float* rope_cos, const float* rope_sin, const HyRows& r, cudaStream_t s);
+// Matrix memory.  gates [T, ldg] fp32 = [W_i h + b_i | W_f h + b_f] (heads each).  hy_mlstm_gates: log gates i = cap tanh(. / cap),
+// f = logsigmoid(cap tanh(. / cap)); the running maximum m_t = max(f_t + m_(t-1), i_t) per (sequence, head), carried in mstate [slots, heads]
+// (a sequence whose step starts at position 0 starts from m = 0); out: dec[t, h] = exp(f + m_(t-1) - m_t), gin[t, h] = exp(i - m_t), floor_[t, h] = exp(-m_t);
+// mprev [T, heads]: scratch
+cudaError_t hy_mlstm_gates(const float* gates, int ldg, int heads, float cap, float* mstate, float* dec, float* gin, float* floor_, float* mprev, const HyRows& r, cudaStream_t s);
+// qq = q dim^-1/2, kk = gin * k, vv = v
+cudaError_t hy_mlstm_prep(bool f32, int heads, int dim, int vdim, const void* q, const void* k, const void* v, int ld, const float* gin, float* qq, float* kk, float* vv, int T, cudaStream_t s);
 // group-wise RMS norm with a gate: v = o (+ skip[c / skip_block] * xs[t, c]); gate_before ? v *= act(gate) : -; v /= rms over each group of
 // `group` channels; v *= w[c % wlen]; !gate_before ? v *= act(gate) : -.  act: 0 = sigmoid, 1 = silu.
+// w == null: no weight.  den_dot != null: every group's o is first divided by max(|den_dot[t, g]|, den_floor[t, g]) + 1e-6 (the matrix memory's normaliser)
 cudaError_t hy_gated_norm(bool f32, const float* o, int C, int group, const float* w, int wlen, const void* gate, int ld_gate, int gate_before, int act,
-                          const float* skip, int skip_block, const void* xs, int ld_xs, void* out, int ld_out, float eps, int T, cudaStream_t s);
+                          const float* skip, int skip_block, const void* xs, int ld_xs, void* out, int ld_out, float eps, int T, cudaStream_t s,
+                          const float* den_dot = nullptr, const float* den_floor = nullptr);
 
 struct HyRouter { int experts, top, groups, keep; float scale; int kind; };     // kind 0: the sigmoid router below; 1: hy_moe_router_softmax
 // sigmoid router over fp32 logits [T, ldz] with a selection-only correction and group-limited choice: a group's score is the sum of its two
@@ -134,18 +165,23 @@ struct HyRouter { int experts, top, groups, keep; float scale; int kind; };     
 cudaError_t hy_moe_router(const HyRouter& m, const float* logits, int ldz, const float* correction, int32_t* idx, float* wgt, int T, cudaStream_t s);
 // router whose weights are the softmax over the chosen logits only: z = logits + bias (fp32), the `top` largest (ties -> lower index), wgt = softmax of those
 cudaError_t hy_moe_router_softmax(const HyRouter& m, const float* logits, int ldz, const float* bias, int32_t* idx, float* wgt, int T, cudaStream_t s);
+// router without scores: token id -> its `top` experts from table [vocab, top], weight 1 / top each.  shared >= 0: one more choice for every
+// token, expert `shared` with weight sigmoid(w_sg . h[t]) (fp32 sum).  idx / wgt: [T, top (+ 1)]
+cudaError_t hy_moe_router_table(bool f32, const int32_t* tokens, const int32_t* table, int vocab, int top, int shared, const void* h, int ldh, const void* w_sg, int W,
+                                int32_t* idx, float* wgt, int T, cudaStream_t s);
 // routed experts, one (token, choice) at a time (decode-sized batches and the fp32 mode).  relu2 == 0: SwiGLU, gu: [E][2 ffp][ldw] with gate / up
 // rows interleaved in blocks of 16; relu2 == 1: act = relu(up h)^2, gu: [E][ffp][ldw] (up rows only).  down: [E][W][ffp]; act: [T * top, ffp]
 cudaError_t hy_moe_gate_up(bool f32, int relu2, const void* h, int ldh, const void* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, void* act, int T, cudaStream_t s);
-cudaError_t hy_moe_down(bool f32, const void* act, const void* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x, int T, cudaStream_t s);
+// x[t] = beta * x[t] + sum over choices
+cudaError_t hy_moe_down(bool f32, const void* act, const void* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x, int T, cudaStream_t s, float beta = 1.f);
 
 // grouped (tensor-core) expert path: rows sorted by expert into 128-row tiles
 // counts -> tile table: tile_expert[n_tiles], row_src[max_tiles * 128] (token * top + choice, or -1), dst_of[T * top]; n_tiles_out holds the tile
 // count at [0] and 2 * experts words of scratch from [4]
 cudaError_t hy_moe_plan(const int32_t* idx, int T, int top, int experts, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out, int32_t* dst_of, int max_tiles, cudaStream_t s);
 cudaError_t hy_moe_gather(const void* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, void* out, int max_tiles, cudaStream_t s);
-// x[t] += sum over choices (in order) wgt[t,c] * y[dst_of[t*top+c]]
-cudaError_t hy_moe_combine(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W, int T, cudaStream_t s);
+// x[t] = beta * x[t] + sum over choices (in order) wgt[t,c] * y[dst_of[t*top+c]]
+cudaError_t hy_moe_combine(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W, int T, cudaStream_t s, float beta = 1.f);
 
 cudaError_t hy_gather_rows_f32(const float* x, const int32_t* rows, float* out, int n, int W, cudaStream_t s);
 // softcap > 0: logits <- softcap * tanh(logits / softcap), in place, before the arg-max (ties -> lowest id)

@@ -110,6 +110,18 @@ std::vector<float> HybridModel::vec(const std::string& name, int n, float init_m
     }
     return v;
 }
+bool HybridModel::has_tensor(const std::string& name) const { return st_ && st_->st.has(name); }
+int HybridModel::rope_table(float base, int dims) {        // cos / sin of position * base^(-2 i / dims), angles in double, [max_seq_len, dims / 2]
+    for (size_t i = 0; i < ropes_.size(); ++i) if (ropes_[i].base == base && ropes_[i].dims == dims) return (int)i;
+    RopeTable rt; rt.base = base; rt.dims = dims; const int half = dims / 2;
+    std::vector<float> cs((size_t)opt.max_seq_len * std::max(1, half)), sn(cs.size());
+    for (int i = 0; i < half; ++i) {
+        const double f = std::pow((double)base, -2.0 * i / (double)dims);
+        for (int ps = 0; ps < opt.max_seq_len; ++ps) { cs[(size_t)ps * half + i] = (float)std::cos(ps * f); sn[(size_t)ps * half + i] = (float)std::sin(ps * f); }
+    }
+    rt.cos = upload_f32(cs); rt.sin = upload_f32(sn); ropes_.push_back(rt);
+    return (int)ropes_.size() - 1;
+}
 static void append_rows(std::vector<float>& dst, int& rows, int K, const std::vector<float>& src, int src_rows, int align) {
     while (rows % align) { dst.resize(dst.size() + K, 0.f); ++rows; }
     dst.insert(dst.end(), src.begin(), src.end()); rows += src_rows;
@@ -136,12 +148,12 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     final_norm_ = upload_f32(vec("final.norm", W, 1.f, 0.1f));
     if (hc_.loop_times > 0) { loop_in_ = upload_mat(tensor("loop.in", W, 2 * W)); loop_step_ = upload_f32(vec("loop.step", hc_.loop_times * W, 0.f, 0.1f)); }
     lw_.resize(hc_.layers.size());
-    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1, max_ffp = 16, max_lat_heads = 1, max_kv = 0, max_Eattn = 8;
+    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1, max_ffp = 16, max_lat_heads = 1, max_kv = 0, max_Eattn = 8, max_mix2 = 0, max_gates = 0;
     for (size_t li = 0; li < hc_.layers.size(); ++li) {
         const HyLayer& l = hc_.layers[li]; LayerW& w = lw_[li];
         const std::string p = "l" + std::to_string(li) + ".", mx = p + "mix.";
         w.norm1 = upload_f32(vec(p + "norm1", W, 1.f, 0.1f));
-        if (hc_.two_norms && l.moe.present) w.norm2 = upload_f32(vec(p + "norm2", W, 1.f, 0.1f));
+        if ((hc_.two_norms || hc_.post_norm) && (l.moe.present || (hc_.post_norm && has_tensor(p + "norm2")))) w.norm2 = upload_f32(vec(p + "norm2", W, 1.f, 0.1f));
         HostMat in; in.K = W; int rows = 0;
         if (l.type == HY_WINDOW_ATTENTION) {
             // fused input projection [q | k | v | gate] (k, v only where the layer fills a cache of its own), each segment on a multiple of 8 rows
@@ -172,6 +184,55 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
             }
             w.o = upload_mat(tensor(mx + "o", W, l.heads * l.vdim));
             max_mix = std::max(max_mix, l.heads * l.vdim);
+        } else if (l.type == HY_LINEAR_ATTENTION || l.type == HY_ATTENTION_BESIDE_MEMORY) {
+            // fused input projection, every segment on a multiple of 8 rows: [q | k | v | gate (| a1)] of the linear-attention side, and for a
+            // layer with attention beside it [q | k | v] of that side (with their biases) in front
+            const HyLinear& n = l.lin; const bool two = l.type == HY_ATTENTION_BESIDE_MEMORY;
+            const std::string lx = two ? mx + "right." : mx;
+            const int qk = n.heads * n.dim, vd = n.heads * n.vdim;
+            std::vector<float> bias;
+            auto seg = [&](const std::string& nm, int nrows, bool biased) -> int {
+                while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
+                const int off = rows;
+                append_rows(in.v, rows, W, tensor(nm, nrows, W).v, nrows, 1);
+                if (two) { bias.resize(off, 0.f); std::vector<float> b = biased ? vec(nm + ".b", nrows, 0.f, 0.2f) : std::vector<float>(nrows, 0.f); bias.insert(bias.end(), b.begin(), b.end()); }
+                return off;
+            };
+            if (two) {
+                if (!hy_win_supported(HyWinAttn{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, 0.f, 1.f}))
+                    throw std::runtime_error("config.json: attention sizes beyond what the kernels hold (vdim <= 256)");
+                w.off_lq = seg(mx + "left.q", l.heads * l.dim, true); w.off_lk = seg(mx + "left.k", l.kv_heads * l.dim, true); w.off_lv = seg(mx + "left.v", l.kv_heads * l.vdim, true);
+                w.q_norm = upload_f32(vec(mx + "left.q.norm", l.heads * l.dim, 1.f, 0.1f)); w.k_norm = upload_f32(vec(mx + "left.k.norm", l.kv_heads * l.dim, 1.f, 0.1f));
+                w.o2 = upload_mat(tensor(mx + "left.o", W, l.heads * l.vdim)); w.o2_bias = upload_f32(vec(mx + "left.o.b", W, 0.f, 0.1f));
+                w.out_w1 = upload_f32(vec(mx + "left.out", W, 1.f, 0.1f)); w.out_w2 = upload_f32(vec(mx + "right.out", W, 1.f, 0.1f));
+                max_mix2 = std::max(max_mix2, l.heads * l.vdim);
+            }
+            w.off_q = seg(lx + "q", qk, false); w.off_k = seg(lx + "k", qk, false); w.off_v = seg(lx + "v", vd, false); w.off_g = seg(lx + "g", vd, false);
+            if (n.kind == HY_LIN_CHANNEL_DECAY) {
+                HostMat a1 = tensor(lx + "a1", st_ ? (int)st_->st.get(lx + "a1").shape[0] : std::max(8, W / 16), W);
+                while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
+                w.off_a1 = rows; w.a_rank = a1.N; append_rows(in.v, rows, W, a1.v, a1.N, 1);
+                w.a2 = upload_mat(tensor(lx + "a2", qk, w.a_rank)); w.a2_bias = upload_f32(vec(lx + "a2.b", qk, 1.f, 1.f));
+            }
+            if (n.kind == HY_LIN_HEAD_DECAY) {
+                w.decay = upload_f32(n.decay);
+                if (n.rot_dims > 0) w.rope = rope_table(n.rot_base, n.rot_dims);
+            }
+            if (n.kind == HY_LIN_MATRIX_MEMORY) {       // log gates: their own small product with an fp32 result, [W_i ; W_f] and [b_i | b_f]
+                HostMat g; g.K = W; int gr = 0;
+                append_rows(g.v, gr, W, tensor(lx + "i", n.heads, W).v, n.heads, 1); append_rows(g.v, gr, W, tensor(lx + "f", n.heads, W).v, n.heads, 1);
+                while (gr % 8) { g.v.resize(g.v.size() + W, 0.f); ++gr; }
+                g.N = gr; w.gates = upload_mat(g);
+                std::vector<float> gb = vec(lx + "i.b", n.heads, 0.f, 0.5f), fb = vec(lx + "f.b", n.heads, 2.f, 1.f);
+                gb.insert(gb.end(), fb.begin(), fb.end()); gb.resize(gr, 0.f);
+                w.gates_bias = upload_f32(gb); max_gates = std::max(max_gates, gr);
+            }
+            if (n.norm == HY_LIN_NORM_HEAD_WEIGHT) w.norm_w = upload_f32(vec(lx + "norm", n.vdim, 1.f, 0.1f));
+            else if (n.norm == HY_LIN_NORM_ALL_WEIGHT) w.norm_w = upload_f32(vec(lx + "norm", vd, 1.f, 0.1f));
+            if (two) { bias.resize(up8(rows), 0.f); w.in_bias = upload_f32(bias); w.in_bias_act = upload_act(bias); }
+            w.o = upload_mat(tensor(lx + "o", W, vd));
+            max_mix = std::max(max_mix, vd); max_qk = std::max(max_qk, qk); max_v = std::max(max_v, vd);
+            max_dec = std::max(max_dec, n.kind == HY_LIN_CHANNEL_DECAY ? qk : n.heads); max_h = std::max(max_h, n.heads);
         } else if (l.type == HY_LATENT_ATTENTION) {
             const int qd = l.heads * (l.dim + l.rot_dim), E = l.kv_rank + l.rot_dim;
             append_rows(in.v, rows, W, tensor(mx + "q", qd, W).v, qd, 1); w.off_a = 0;
@@ -204,16 +265,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
                 }
                 if (!all) { w.uk_heads.clear(); w.uv_heads.clear(); }
             }
-            for (size_t i = 0; i < ropes_.size(); ++i) if (ropes_[i].base == l.rot_base && ropes_[i].dims == l.rot_dims) w.rope = (int)i;
-            if (w.rope < 0) {
-                RopeTable rt; rt.base = l.rot_base; rt.dims = l.rot_dims; const int half = l.rot_dims / 2;
-                std::vector<float> cs((size_t)opt.max_seq_len * std::max(1, half)), sn(cs.size());
-                for (int i = 0; i < half; ++i) {
-                    const double f = std::pow((double)l.rot_base, -2.0 * i / (double)l.rot_dims);
-                    for (int ps = 0; ps < opt.max_seq_len; ++ps) { cs[(size_t)ps * half + i] = (float)std::cos(ps * f); sn[(size_t)ps * half + i] = (float)std::sin(ps * f); }
-                }
-                rt.cos = upload_f32(cs); rt.sin = upload_f32(sn); w.rope = (int)ropes_.size(); ropes_.push_back(rt);
-            }
+            w.rope = rope_table(l.rot_base, l.rot_dims);
             max_Eattn = std::max(max_Eattn, E); max_lat_heads = std::max(max_lat_heads, l.heads); max_qabs = std::max(max_qabs, l.heads * E); max_lat = std::max(max_lat, l.heads * l.kv_rank); max_mix = std::max(max_mix, l.heads * l.vdim);
         } else if (l.type == HY_CHANNEL_DELTA) {
             const int qk = l.kv_heads * l.dim, vd = l.heads * l.vdim;
@@ -250,40 +302,65 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         }
         in.N = rows; w.in = upload_mat(in);
         max_in = std::max(max_in, up8(rows));
-        if (l.moe.present) {
+        if (l.moe.present && l.moe.dense) {
+            const std::string mp = p + "mlp.";
+            w.up = upload_mat(tensor(mp + "up", l.moe.ff, W)); w.dn = upload_mat(tensor(mp + "down", W, l.moe.ff));
+            max_act = std::max(max_act, up8(l.moe.ff));
+        } else if (l.moe.present) {
             const HyMoe& m = l.moe; const std::string mp = p + "mlp.";
+            w.n_exp = m.experts + (m.shared_ff > 0 ? 1 : 0); w.n_top = m.top + (m.shared_ff > 0 ? 1 : 0); w.ff_max = std::max(m.ff, m.shared_ff);
+            if (m.router == HY_ROUTER_TOKEN_TABLE) {
+                std::vector<int32_t> tb((size_t)V * m.top);
+                if (st_) {
+                    const StTensor& t = st_->st.get(mp + "table");
+                    if (t.dtype != "I32" || t.shape.size() != 2 || t.shape[0] != V || t.shape[1] != m.top) throw std::runtime_error("checkpoint tensor " + mp + "table does not have the shape the configuration implies");
+                    std::memcpy(tb.data(), t.data, tb.size() * 4);
+                } else {
+                    uint64_t sd = name_hash(mp + "table", cfg.seed);
+                    for (int v = 0; v < V; ++v) {       // `top` different experts per token id: consecutive ones from a random first
+                        const int first = std::min(m.experts - 1, (int)((unit_rand(sd) * 0.5f + 0.5f) * (float)m.experts));
+                        for (int c = 0; c < m.top; ++c) tb[(size_t)v * m.top + c] = (first + c) % m.experts;
+                    }
+                }
+                for (int32_t e : tb) if (e < 0 || e >= m.experts) throw std::runtime_error("checkpoint tensor " + mp + "table names an expert that does not exist");
+                w.table = (int32_t*)dmalloc(tb.size() * 4);
+                cuda_check(cudaMemcpy(w.table, tb.data(), tb.size() * 4, cudaMemcpyHostToDevice), "H2D");
+                if (m.shared_ff > 0) { std::vector<float> sg = tensor(mp + "shared.sg", 1, W).v; sg.resize(Wld_, 0.f); w.shared_gate = upload_act(sg); }
+            } else {
             w.router = upload_mat(tensor(mp + "router", m.experts, W));
             if (m.router == HY_ROUTER_SOFTMAX_CHOSEN) w.router_bias = upload_f32(vec(mp + "router.b", m.experts, 0.f, 0.05f));
             else w.correction = upload_f32(vec(mp + "correction", m.experts, 0.f, 0.05f));
-            w.ffp = up16(m.ff);
+            }
+            w.ffp = up16(w.ff_max);
             // first-stage rows per expert: SwiGLU experts hold gate and up rows interleaved in blocks of 16, gate-less experts their up rows
             const int rows1 = m.act == HY_EXPERT_RELU2 ? w.ffp : 2 * w.ffp;
-            std::vector<float> gu((size_t)m.experts * rows1 * Wld_, 0.f), dn((size_t)m.experts * W * w.ffp, 0.f);
-            for (int e = 0; e < m.experts; ++e) {
-                const std::string ep = mp + "e" + std::to_string(e) + ".";
-                HostMat u = tensor(ep + "up", m.ff, W), d = tensor(ep + "down", W, m.ff);
+            std::vector<float> gu((size_t)w.n_exp * rows1 * Wld_, 0.f), dn((size_t)w.n_exp * W * w.ffp, 0.f);
+            for (int e = 0; e < w.n_exp; ++e) {
+                const bool shared = e == m.experts; const int eff = shared ? m.shared_ff : m.ff;       // the shared expert is stored behind the routed ones, rows beyond its width stay zero
+                const std::string ep = shared ? mp + "shared." : mp + "e" + std::to_string(e) + ".";
+                HostMat u = tensor(ep + "up", eff, W), d = tensor(ep + "down", W, eff);
                 if (m.act == HY_EXPERT_RELU2) {
-                    for (int f = 0; f < m.ff; ++f) std::memcpy(&gu[((size_t)e * w.ffp + f) * Wld_], &u.v[(size_t)f * W], (size_t)W * 4);
+                    for (int f = 0; f < eff; ++f) std::memcpy(&gu[((size_t)e * w.ffp + f) * Wld_], &u.v[(size_t)f * W], (size_t)W * 4);
                 } else {
-                    HostMat g = tensor(ep + "gate", m.ff, W);
-                    for (int f = 0; f < m.ff; ++f) {
+                    HostMat g = tensor(ep + "gate", eff, W);
+                    for (int f = 0; f < eff; ++f) {
                         const size_t pg = ((size_t)e * 2 * w.ffp + (size_t)(f >> 4) * 32 + (f & 15)) * Wld_;
                         std::memcpy(&gu[pg], &g.v[(size_t)f * W], (size_t)W * 4); std::memcpy(&gu[pg + (size_t)16 * Wld_], &u.v[(size_t)f * W], (size_t)W * 4);
                     }
                 }
-                for (int n = 0; n < W; ++n) std::memcpy(&dn[((size_t)e * W + n) * w.ffp], &d.v[(size_t)n * m.ff], (size_t)m.ff * 4);
+                for (int n = 0; n < W; ++n) std::memcpy(&dn[((size_t)e * W + n) * w.ffp], &d.v[(size_t)n * eff], (size_t)eff * 4);
             }
             w.gu = upload_act(gu); w.down = upload_act(dn);
             if (!f32_ && opt.hy_tensor_core && W % 8 == 0) {
                 w.moe_tc = true;
                 for (int i = 0; i < 2; ++i) {
                     const uint32_t bn = i ? 256 : 128;
-                    if (make_tmap_bf16_2d(&w.tm_gu[i], w.gu, (uint64_t)m.experts * rows1, (uint64_t)Wld_, (uint64_t)Wld_, bn, 64) != 0 ||
-                        make_tmap_bf16_2d(&w.tm_down[i], w.down, (uint64_t)m.experts * W, (uint64_t)w.ffp, (uint64_t)w.ffp, bn, 64) != 0) w.moe_tc = false;
+                    if (make_tmap_bf16_2d(&w.tm_gu[i], w.gu, (uint64_t)w.n_exp * rows1, (uint64_t)Wld_, (uint64_t)Wld_, bn, 64) != 0 ||
+                        make_tmap_bf16_2d(&w.tm_down[i], w.down, (uint64_t)w.n_exp * W, (uint64_t)w.ffp, (uint64_t)w.ffp, bn, 64) != 0) w.moe_tc = false;
                 }
             }
             max_ffp = std::max(max_ffp, w.ffp);
-            max_act = std::max(max_act, m.top * w.ffp); max_top = std::max(max_top, m.top); max_E = std::max(max_E, m.experts);
+            max_act = std::max(max_act, w.n_top * w.ffp); max_top = std::max(max_top, w.n_top); max_E = std::max(max_E, w.n_exp);
         }
     }
     delete st_; st_ = nullptr;
@@ -309,6 +386,12 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         tile_expert_ = (int32_t*)dmalloc((size_t)max_tiles_ * 4); row_src_ = (int32_t*)dmalloc((size_t)max_tiles_ * 128 * 4);
         n_tiles_ = (int32_t*)dmalloc((size_t)(4 + 2 * max_E) * 4); dst_of_ = (int32_t*)dmalloc(MR * max_top * 4);
     }
+    if (hc_.post_norm) { y_ = (float*)dmalloc(MR * W * 4); y2_ = (float*)dmalloc(MR * W * 4); }
+    if (max_mix2 > 0) { ld_mix2_ = up8(max_mix2); mix2_ = dmalloc(MR * ld_mix2_ * es_); }
+    if (max_gates > 0) {
+        ld_gates_ = max_gates; gates_ = (float*)dmalloc(MR * ld_gates_ * 4);
+        gin_ = (float*)dmalloc(MR * max_h * 4); floor_ = (float*)dmalloc(MR * max_h * 4); mprev_ = (float*)dmalloc(MR * max_h * 4); ndot_ = (float*)dmalloc(MR * max_h * 4);
+    }
     hs_ = dmalloc((size_t)MS_ * Wld_ * es_); d_out_ids_ = (int32_t*)dmalloc((size_t)MS_ * 4);
     logits_ = (float*)dmalloc((size_t)opt.max_batch * V * 4);      // own logits: sampling steps only (one row per sequence)
     cuda_check(cudaMallocHost(&h_out_ids, (size_t)MS_ * 4), "cudaMallocHost");
@@ -327,12 +410,16 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     }
     max_pages_per_seq = opt.max_seq_len / 64;
     if (num_pages < 1) throw std::runtime_error("cache pool too small");
-    caches_.resize(hc_.n_caches); states_.resize(hc_.n_states); tails_.resize(hc_.n_states);
+    caches_.resize(hc_.n_caches); states_.resize(hc_.n_states); tails_.resize(hc_.n_states); aux_.resize(hc_.n_states);
     state_slots = hc_.n_states > 0 ? opt.max_batch : 0;
     for (const HyRun& r : hc_.runs) {
         const HyLayer& l = hc_.layers[r.layer];
         if (r.cache_owner) { const size_t b = (size_t)num_pages * 64 * cache_row_width(l) * es_; caches_[r.cache_idx] = dmalloc(b); kv_pool_bytes += b; }
-        else if (r.state_idx >= 0) {
+        if (r.state_idx >= 0 && (l.type == HY_LINEAR_ATTENTION || l.type == HY_ATTENTION_BESIDE_MEMORY)) {
+            const HyLinear& n = l.lin;
+            states_[r.state_idx] = (float*)dmalloc((size_t)state_slots * n.heads * n.dim * n.vdim * 4);
+            if (n.kind == HY_LIN_MATRIX_MEMORY) aux_[r.state_idx] = (float*)dmalloc((size_t)state_slots * n.heads * (n.dim + 1) * 4);
+        } else if (r.state_idx >= 0) {
             const int sd = l.type == HY_CHANNEL_DELTA ? l.dim : l.state;
             states_[r.state_idx] = (float*)dmalloc((size_t)state_slots * l.heads * sd * l.vdim * 4);
             tails_[r.state_idx] = dmalloc((size_t)state_slots * std::max(1, l.conv - 1) * lw_[r.layer].conv_ch * es_);
@@ -344,7 +431,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     for (const HyLayer& l : hc_.layers) if (l.type == HY_LATENT_ATTENTION) meta_cap_words_ += 3 * ((MR / 64 + (size_t)opt.max_batch) * l.heads + 8) + (size_t)opt.max_batch + 8;
     split_slots_ = std::min(16 * opt.max_batch, 4096);
     for (const HyLayer& l : hc_.layers) if (l.type == HY_LATENT_ATTENTION) meta_cap_words_ += 5 * (MR * l.heads / HY_MLA_TILE_QUERIES + (size_t)opt.max_batch + (size_t)split_slots_ + 8) + 3 * ((size_t)opt.max_batch + 4);
-    for (const HyLayer& l : hc_.layers) if (l.type == HY_WINDOW_ATTENTION) meta_cap_words_ += 2 * (MR * (size_t)(l.heads / l.kv_heads) / HY_WIN_TILE_QUERIES + 2 * (size_t)opt.max_batch + 16);
+    for (const HyLayer& l : hc_.layers) if (l.type == HY_WINDOW_ATTENTION || l.type == HY_ATTENTION_BESIDE_MEMORY) meta_cap_words_ += 2 * (MR * (size_t)(l.heads / l.kv_heads) / HY_WIN_TILE_QUERIES + 2 * (size_t)opt.max_batch + 16);
     if (hc_.n_caches > 0 && !f32_) { split_o_ = (float*)dmalloc((size_t)split_slots_ * max_lat * 4); split_ml_ = (float*)dmalloc((size_t)split_slots_ * max_lat_heads * 2 * 4); }
     for (int i = 0; i < 2; ++i) {
         cuda_check(cudaMallocHost(&h_meta_buf_[i], meta_cap_words_ * 4), "cudaMallocHost meta");
@@ -373,37 +460,46 @@ static int pick_tile_n(int M, int N, int sms) {
 }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-void HybridModel::gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha, const void* bias_act) {
+void HybridModel::gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha, const void* bias_act, int act) {
     // bf16: the framework's tcgen05 tile GEMM (TMA operands, fp32 accumulator in TMEM) wherever pitches and pointers fit its 16-byte rules;
     // a bf16 store may write the columns up to N rounded up to 8 (every such output has that room), an fp32 output needs N itself to fit
     bool tc = B.tc && !f32_ && lda % 8 == 0 && aligned16(A) && lda >= B.ld;
     if (mode == HY_STORE) tc = tc && ldc % 8 == 0 && aligned16(C) && (!bias || (bias_act && aligned16(bias_act))) && alpha == 1.f;     // a bias in the activation type, padded to N rounded up to 8
-    else tc = tc && B.N % 8 == 0 && ldc % 4 == 0 && aligned16(C) && (!bias || aligned16(bias));
+    else tc = tc && B.N % 8 == 0 && ldc % 4 == 0 && aligned16(C) && (!bias || aligned16(bias)) && act == 0;
     CUtensorMap tmA;
     if (tc && make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)B.ld, (uint64_t)lda, 128, 64) != 0) tc = false;
-    if (!tc) { cuda_check(hy_gemm(f32_, mode, A, lda, B.p, B.ld, C, ldc, M, B.N, B.K, bias, alpha, 1, 0, 0, 0, stream), "gemm"); return; }
+    if (!tc) { cuda_check(hy_gemm(f32_, mode, A, lda, B.p, B.ld, C, ldc, M, B.N, B.K, bias, alpha, 1, 0, 0, 0, stream, act), "gemm"); return; }
     GemmParams g{}; g.M = M; g.N = up8(B.N); g.K = B.ld;
     const int bn = pick_tile_n(M, g.N, sm_count);
-    if (mode == HY_STORE) { g.out = C; g.ldo = ldc; g.bias = bias ? bias_act : nullptr; cuda_check(launch_gemm(&tmA, &B.tm[bn == 32 ? 0 : bn == 64 ? 1 : bn == 128 ? 2 : 3], g, EPI_STORE, bn, stream), "gemm (tcgen05)"); return; }
+    if (mode == HY_STORE) { g.out = C; g.ldo = ldc; g.bias = bias ? bias_act : nullptr; g.store_act = act; cuda_check(launch_gemm(&tmA, &B.tm[bn == 32 ? 0 : bn == 64 ? 1 : bn == 128 ? 2 : 3], g, EPI_STORE, bn, stream), "gemm (tcgen05)"); return; }
     g.f32_out = reinterpret_cast<float*>(C); g.ldf = ldc; g.f32_accumulate = mode == HY_ACC_F32; g.alpha = alpha; g.bias_f32 = bias;
     cuda_check(launch_gemm(&tmA, &B.tm[bn == 32 ? 0 : bn == 64 ? 1 : bn == 128 ? 2 : 3], g, EPI_F32, bn, stream), "gemm (tcgen05, fp32 out)");
 }
 
-void HybridModel::moe(const LayerW& w, const HyLayer& l, const void* h_in, const HyRows& r, const std::function<void(int)>& MARK) {
+void HybridModel::moe(const LayerW& w, const HyLayer& l, const void* h_in, const HyRows& r, const std::function<void(int)>& MARK, const int32_t* tokens, float beta) {
     const HyMoe& m = l.moe; const int W = hc_.width, T = r.T;
     const bool relu2 = m.act == HY_EXPERT_RELU2; const int rows1 = relu2 ? w.ffp : 2 * w.ffp;
+    if (m.dense) {        // one feed-forward for every row: up product with the activation in its epilogue, down product into the sublayer's fp32 output
+        gemm(HY_STORE, h_in, Wld_, w.up, act_, up8(m.ff), T, nullptr, 1.f, nullptr, relu2 ? 1 : 0); MARK(25);
+        gemm(HY_STORE_F32, act_, up8(m.ff), w.dn, y_, W, T, nullptr, 1.f); MARK(26);
+        return;
+    }
     HyRouter hr{m.experts, m.top, m.groups, m.keep, m.scale, m.router};
-    // router logits: bf16 (or fp32) inputs, exact products, fp32 accumulation and output
-    gemm(HY_STORE_F32, h_in, Wld_, w.router, rlog_, m.experts, T, nullptr, 1.f);
-    if (m.router == HY_ROUTER_SOFTMAX_CHOSEN) cuda_check(hy_moe_router_softmax(hr, rlog_, m.experts, w.router_bias, idx_, wgt_, T, stream), "router");
-    else cuda_check(hy_moe_router(hr, rlog_, m.experts, w.correction, idx_, wgt_, T, stream), "router");
+    if (m.router == HY_ROUTER_TOKEN_TABLE) {
+        cuda_check(hy_moe_router_table(f32_, tokens, w.table, hc_.vocab, m.top, m.shared_ff > 0 ? m.experts : -1, h_in, Wld_, w.shared_gate, W, idx_, wgt_, T, stream), "router (table)");
+    } else {
+        // router logits: bf16 (or fp32) inputs, exact products, fp32 accumulation and output
+        gemm(HY_STORE_F32, h_in, Wld_, w.router, rlog_, m.experts, T, nullptr, 1.f);
+        if (m.router == HY_ROUTER_SOFTMAX_CHOSEN) cuda_check(hy_moe_router_softmax(hr, rlog_, m.experts, w.router_bias, idx_, wgt_, T, stream), "router");
+        else cuda_check(hy_moe_router(hr, rlog_, m.experts, w.correction, idx_, wgt_, T, stream), "router");
+    }
     MARK(12);
     if (w.moe_tc && T >= opt.hy_moe_grouped_rows) {
         // prefill-sized batches: rows sorted by expert into 128-row tiles, two grouped tcgen05 GEMMs (SwiGLU in the first one's epilogue),
         // then each token adds its choices' rows in choice order
-        const int bound = std::min(max_tiles_, (T * m.top + 127) / 128 + std::min(m.experts, T * m.top));
-        cuda_check(hy_moe_plan(idx_, T, m.top, m.experts, tile_expert_, row_src_, n_tiles_, dst_of_, bound, stream), "expert plan");
-        cuda_check(hy_moe_gather(h_in, Wld_, Wld_, row_src_, n_tiles_, m.top, moe_a_, bound, stream), "expert gather"); MARK(16);
+        const int bound = std::min(max_tiles_, (T * w.n_top + 127) / 128 + std::min(w.n_exp, T * w.n_top));
+        cuda_check(hy_moe_plan(idx_, T, w.n_top, w.n_exp, tile_expert_, row_src_, n_tiles_, dst_of_, bound, stream), "expert plan");
+        cuda_check(hy_moe_gather(h_in, Wld_, Wld_, row_src_, n_tiles_, w.n_top, moe_a_, bound, stream), "expert gather"); MARK(16);
         CUtensorMap tmA, tmB;
         if (make_tmap_bf16_2d(&tmA, moe_a_, (uint64_t)bound * 128, (uint64_t)Wld_, (uint64_t)Wld_, 128, 64) != 0 ||
             make_tmap_bf16_2d(&tmB, act_, (uint64_t)bound * 128, (uint64_t)w.ffp, (uint64_t)w.ffp, 128, 64) != 0) throw std::runtime_error("tensor map for the expert activations failed");
@@ -415,19 +511,52 @@ void HybridModel::moe(const LayerW& w, const HyLayer& l, const void* h_in, const
         d.m_tile_group = tile_expert_; d.n_m_tiles = n_tiles_; d.group_rows = W;
         const int bn2 = W >= 256 ? 256 : 128;
         cuda_check(launch_gemm(&tmB, &w.tm_down[bn2 == 256], d, EPI_F32, bn2, stream), "experts down (grouped tcgen05)"); MARK(18);
-        cuda_check(hy_moe_combine(moe_y_, W, dst_of_, wgt_, m.top, x_, W, T, stream), "expert combine"); MARK(19);
+        cuda_check(hy_moe_combine(moe_y_, W, dst_of_, wgt_, w.n_top, x_, W, T, stream, beta), "expert combine"); MARK(19);
         return;
     }
-    cuda_check(hy_moe_gate_up(f32_, relu2, h_in, Wld_, w.gu, Wld_, W, m.ff, w.ffp, idx_, m.top, act_, T, stream), "experts first stage");
-    cuda_check(hy_moe_down(f32_, act_, w.down, W, w.ffp, idx_, wgt_, m.top, x_, T, stream), "experts down"); MARK(13);
+    cuda_check(hy_moe_gate_up(f32_, relu2, h_in, Wld_, w.gu, Wld_, W, w.ff_max, w.ffp, idx_, w.n_top, act_, T, stream), "experts first stage");
+    cuda_check(hy_moe_down(f32_, act_, w.down, W, w.ffp, idx_, wgt_, w.n_top, x_, T, stream, beta), "experts down"); MARK(13);
 }
 
 const char* HybridModel::kt_name(int id) const {
     static const char* n[32] = {"h2d+embed", "layer_norm", "in_proj_gemm", "latent_absorb+up_gemm", "latent_cache_write", "latent_attention", "conv", "recurrence_prep",
                                 "recurrence", "gated_norm", "low_rank_gemm", "out_proj_gemm", "router", "experts_per_token", "loop_in", "head+argmax",
                                 "expert_plan+gather", "expert_gate_up_gemm", "expert_down_gemm", "expert_combine", "context_gather+kv_up_gemm", "attention_prefill_form", "rms_norm", "window_qk_norm+cache_write",
-                                "window_attention", "", "", "", "", "", "", ""};
+                                "window_attention", "dense_ff_up_gemm", "dense_ff_down_gemm", "post_norm", "linear_attention_prep", "memory_gates", "", ""};
     return n[id & 31];
+}
+
+static HyWinAttn win_params(const HyLayer& l, float lambda) {
+    HyWinAttn a{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, lambda, 1.f - l.diff};
+    a.softcap = l.softcap; a.slope_exp = l.slope_exp; a.q_temp_coef = l.q_temp_coef; a.q_temp_every = l.q_temp_every;
+    return a;
+}
+
+// The linear-attention side of a layer: operands from the fused input projection (proj_), the recurrence on the sequence's state slot, the
+// per-head norm and output gate; leaves the output projection's input in mix_.
+void HybridModel::linear_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const std::function<void(int)>& MARK) {
+    const HyLinear& n = l.lin; const int H = n.heads, D = n.dim, VD = n.vdim, T = r.T;
+    auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
+    const void *q = at(proj_, w.off_q), *k = at(proj_, w.off_k), *v = at(proj_, w.off_v), *g = at(proj_, w.off_g);
+    float* st = states_[run.state_idx];
+    if (n.kind == HY_LIN_CHANNEL_DECAY) {
+        gemm(HY_STORE_F32, at(proj_, w.off_a1), ld_proj_, w.a2, dec_, H * D, T, w.a2_bias, 1.f); MARK(10);       // the decay's pre-activation in fp32
+        cuda_check(hy_lin_prep(f32_, HyLinPrep{H, D, VD, n.q_scaled, n.k_scaled, 0}, q, k, v, ld_proj_, qq_, kk_, vv_, dec_, n.tau, nullptr, nullptr, nullptr, nullptr, r, stream), "linear attention operands"); MARK(28);
+        cuda_check(hy_recurrence(HY_REC_CHANNEL, qq_, kk_, vv_, dec_, nullptr, rec_, st, H, H, D, VD, r, stream), "gated linear attention"); MARK(8);
+        cuda_check(hy_gated_norm(f32_, rec_, H * VD, VD, w.norm_w, VD, g, ld_proj_, 0, n.gate_silu, nullptr, 1, nullptr, 0, mix_, ld_mix_, hc_.eps, T, stream), "gated norm"); MARK(9);
+    } else if (n.kind == HY_LIN_HEAD_DECAY) {
+        const float* rc = w.rope >= 0 ? ropes_[w.rope].cos : nullptr; const float* rs = w.rope >= 0 ? ropes_[w.rope].sin : nullptr;
+        cuda_check(hy_lin_prep(f32_, HyLinPrep{H, D, VD, n.q_scaled, n.k_scaled, n.rot_dims}, q, k, v, ld_proj_, qq_, kk_, vv_, nullptr, 1.f, w.decay, dec_, rc, rs, r, stream), "retention operands"); MARK(28);
+        cuda_check(hy_recurrence(HY_REC_SCALAR, qq_, kk_, vv_, dec_, nullptr, rec_, st, H, H, D, VD, r, stream), "retention"); MARK(8);
+        cuda_check(hy_gated_norm(f32_, rec_, H * VD, VD, nullptr, 1, g, ld_proj_, 0, n.gate_silu, nullptr, 1, nullptr, 0, mix_, ld_mix_, hc_.eps, T, stream), "gated norm"); MARK(9);
+    } else {
+        float* aux = aux_[run.state_idx];
+        gemm(HY_STORE_F32, h_, Wld_, w.gates, gates_, ld_gates_, T, w.gates_bias, 1.f);
+        cuda_check(hy_mlstm_gates(gates_, ld_gates_, H, n.gate_cap, aux + (size_t)state_slots * H * D, dec_, gin_, floor_, mprev_, r, stream), "matrix memory gates"); MARK(29);
+        cuda_check(hy_mlstm_prep(f32_, H, D, VD, q, k, v, ld_proj_, gin_, qq_, kk_, vv_, T, stream), "matrix memory operands"); MARK(28);
+        cuda_check(hy_recurrence(HY_REC_SCALAR, qq_, kk_, vv_, dec_, nullptr, rec_, st, H, H, D, VD, r, stream, aux, ndot_), "matrix memory"); MARK(8);
+        cuda_check(hy_gated_norm(f32_, rec_, H * VD, VD, w.norm_w, H * VD, g, ld_proj_, 0, n.gate_silu, nullptr, 1, nullptr, 0, mix_, ld_mix_, hc_.eps, T, stream, ndot_, floor_), "gated norm"); MARK(9);
+    }
 }
 
 void HybridModel::forward(const StepInput& in, float* logits_out) {
@@ -462,10 +591,9 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     std::vector<TileList> tile_lists(hc_.layers.size());
     for (size_t li = 0; li < hc_.layers.size(); ++li) {
         const HyLayer& l = hc_.layers[li]; TileList& tl = tile_lists[li];
-        if (l.type == HY_WINDOW_ATTENTION) {
+        if (l.type == HY_WINDOW_ATTENTION || l.type == HY_ATTENTION_BESIDE_MEMORY) {
             // windowed attention on the tensor cores: tiles of 64 consecutive (row, head-of-the-group) pairs of one sequence; a decoding row is one tile per key/value head
-            tl.mma = !f32_ && opt.hy_tensor_core && ld_proj_ % 8 == 0 && ld_mix_ % 8 == 0 &&
-                     hy_win_mma_supported(HyWinAttn{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, 0.f, 1.f});
+            tl.mma = !f32_ && opt.hy_tensor_core && ld_proj_ % 8 == 0 && (l.type == HY_WINDOW_ATTENTION ? ld_mix_ : ld_mix2_) % 8 == 0 && hy_win_mma_supported(win_params(l, 0.f));
             if (!tl.mma) continue;
             tile_seq_.clear(); tile_q0_.clear(); ptile_seq_.clear(); ptile_row0_.clear();
             const int group = l.heads / l.kv_heads;
@@ -527,19 +655,57 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
 
     size_t ek = 0;
     if (profile_all) {
-        const size_t need = hc_.runs.size() * 24 + 16;
+        const size_t need = hc_.runs.size() * 32 + 16;
         if (ev_all.size() < need) { size_t o = ev_all.size(); ev_all.resize(need); for (size_t i = o; i < need; ++i) cudaEventCreate(&ev_all[i]); }
         ev_ids.assign(ev_all.size(), 0);
         cudaEventRecord(ev_all[ek++], stream);
     }
     const std::function<void(int)> MARK = [&](int id) { if (profile_all && ek < ev_all.size()) { ev_ids[ek] = id; cudaEventRecord(ev_all[ek++], stream); } };
-    cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, hc_.loop_times > 0 ? x0_ : nullptr, T, W, V, hc_.embed_scale, stream), "embed"); MARK(0);
+    cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, hc_.loop_times > 0 ? x0_ : nullptr, T, W, V, hc_.embed_scale, stream, hc_.post_norm ? h_ : nullptr, Wld_), "embed"); MARK(0);
     auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
     for (const HyRun& run : hc_.runs) {
         const HyLayer& l = hc_.layers[run.layer]; const LayerW& w = lw_[run.layer];
         if (run.first_of_pass) {         // re-injection: x <- W_in [x ; x0] + step[pass]
             cuda_check(hy_concat(f32_, x_, x0_, cat_, T, W, stream), "concat");
             gemm(HY_STORE_F32, cat_, 2 * W, loop_in_, x_, W, T, loop_step_ + (size_t)run.pass * W, 1.f); MARK(14);
+        }
+        if (hc_.post_norm) {
+            // norm after the sum: the sublayers read the residual itself (h_ holds it in the activation type), their outputs come back in fp32
+            // (y_, y2_) and hy_post_norm closes each half: x <- norm(alpha x + sublayer(x))
+            gemm(HY_STORE, h_, Wld_, w.in, proj_, ld_proj_, T, w.in_bias, 1.f, w.in_bias_act); MARK(2);
+            const bool two = l.type == HY_ATTENTION_BESIDE_MEMORY;
+            if (two) {
+                const HyWinAttn a = win_params(l, 0.f);
+                cuda_check(hy_win_prep(f32_, a, at(proj_, w.off_lq), ld_proj_, at(proj_, w.off_lk), at(proj_, w.off_lv), ld_proj_, w.q_norm, w.k_norm, hc_.eps, caches_[run.cache_idx], r, stream),
+                           "query / key norm + cache write"); MARK(23);
+                const TileList& tl = tile_lists[run.layer];
+                if (tl.mma) {
+                    cuda_check(hy_win_attention_mma(a, at(proj_, w.off_lq), ld_proj_, caches_[run.cache_idx], nullptr, nullptr, 0, mix2_, ld_mix2_, hc_.eps, r, d_meta_ + tl.o_wseq, d_meta_ + tl.o_wq0,
+                                                    tl.n_w, stream), "attention (mma)");
+                    cuda_check(hy_win_decode_mma(a, at(proj_, w.off_lq), ld_proj_, caches_[run.cache_idx], nullptr, nullptr, 0, mix2_, ld_mix2_, hc_.eps, r, d_meta_ + tl.o_dseq, d_meta_ + tl.o_dq0,
+                                                 tl.n_d, stream), "attention (mma, decoding rows)");
+                } else cuda_check(hy_win_attention(f32_, a, at(proj_, w.off_lq), ld_proj_, caches_[run.cache_idx], nullptr, nullptr, 0, mix2_, ld_mix2_, hc_.eps, r, stream), "attention");
+                MARK(24);
+                gemm(HY_STORE_F32, mix2_, ld_mix2_, w.o2, y2_, W, T, w.o2_bias, 1.f); MARK(11);
+            }
+            linear_mixer(run, l, w, r, MARK);
+            gemm(HY_STORE_F32, mix_, ld_mix_, w.o, y_, W, T, nullptr, 1.f); MARK(11);
+            if (two) cuda_check(hy_post_norm(f32_, x_, hc_.post_alpha, y2_, w.out_w1, y_, w.out_w2, 0.5f, w.norm1, h_, Wld_, T, W, hc_.eps, stream), "norm after the mixers");
+            else cuda_check(hy_post_norm(f32_, x_, hc_.post_alpha, y_, nullptr, nullptr, nullptr, 1.f, w.norm1, h_, Wld_, T, W, hc_.eps, stream), "norm after the mixer");
+            MARK(27);
+            if (l.moe.present && l.moe.dense) {
+                moe(w, l, h_, r, MARK);
+                cuda_check(hy_post_norm(f32_, x_, hc_.post_alpha, y_, nullptr, nullptr, nullptr, 1.f, w.norm2, h_, Wld_, T, W, hc_.eps, stream), "norm after the feed-forward"); MARK(27);
+            } else if (l.moe.present) {
+                moe(w, l, h_, r, MARK, d_meta_ + o_tok, hc_.post_alpha);      // x <- alpha x + experts, choice by choice
+                cuda_check(hy_post_norm(f32_, x_, 1.f, nullptr, nullptr, nullptr, nullptr, 1.f, w.norm2, h_, Wld_, T, W, hc_.eps, stream), "norm after the experts"); MARK(27);
+            } else if (w.norm2) { cuda_check(hy_post_norm(f32_, x_, hc_.post_alpha, nullptr, nullptr, nullptr, nullptr, 1.f, w.norm2, h_, Wld_, T, W, hc_.eps, stream), "second norm"); MARK(27); }
+            if (capture_layers) {
+                cuda_check(cudaStreamSynchronize(stream), "capture sync");
+                const size_t n0 = capture_layers->size(); capture_layers->resize(n0 + (size_t)T * W);
+                cuda_check(cudaMemcpy(capture_layers->data() + n0, x_, (size_t)T * W * 4, cudaMemcpyDeviceToHost), "capture D2H");
+            }
+            continue;
         }
         if (hc_.norm == HY_RMS_NORM) { cuda_check(hy_rmsnorm_pair(f32_, x_, nullptr, w.norm1, h_, w.norm2, w.norm2 ? h2_ : nullptr, Wld_, T, W, hc_.eps, stream), "rms norm"); MARK(22); }
         else { cuda_check(hy_layernorm(f32_, x_, nullptr, w.norm1, h_, Wld_, T, W, hc_.eps, stream), "layer norm"); MARK(1); }
@@ -597,7 +763,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             gemm(HY_STORE, at(proj_, w.off_c), ld_proj_, w.a2, p2_, ld_p2_, T, nullptr, 1.f);
             gemm(HY_STORE, at(proj_, w.off_d), ld_proj_, w.g2, at(p2_, off_g), ld_p2_, T, nullptr, 1.f); MARK(10);
             cuda_check(hy_delta_prep(f32_, d, conv_, ld_conv_, at(proj_, w.off_b), ld_proj_, p2_, ld_p2_, w.A_log, w.dt_bias, qq_, kk_, vv_, dec_, beta_, T, stream), "delta prep"); MARK(7);
-            cuda_check(hy_recurrence(true, qq_, kk_, vv_, dec_, beta_, rec_, states_[run.state_idx], l.heads, l.kv_heads, l.dim, l.vdim, r, stream), "delta rule"); MARK(8);
+            cuda_check(hy_recurrence(HY_REC_DELTA, qq_, kk_, vv_, dec_, beta_, rec_, states_[run.state_idx], l.heads, l.kv_heads, l.dim, l.vdim, r, stream), "delta rule"); MARK(8);
             cuda_check(hy_gated_norm(f32_, rec_, l.heads * l.vdim, l.vdim, w.norm_w, l.vdim, at(p2_, off_g), ld_p2_, 0, 0, nullptr, 1, nullptr, 0, mix_, ld_mix_, hc_.eps, T, stream), "gated norm"); MARK(9);
         } else {
             const HyMamba m{l.heads, l.vdim, l.state, l.groups};
@@ -605,7 +771,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             cuda_check(hy_conv_silu(f32_, at(proj_, w.off_b), ld_proj_, w.conv_ch, w.conv_w, w.conv_b, l.conv, conv_, ld_conv_, tails_[run.state_idx], r, stream), "conv");
             cuda_check(hy_conv_tails(f32_, at(proj_, w.off_b), ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails"); MARK(6);
             cuda_check(hy_mamba_prep(f32_, m, conv_, ld_conv_, at(proj_, w.off_c), ld_proj_, w.A_log, w.dt_bias, qq_, kk_, vv_, dec_, T, stream), "mamba prep"); MARK(7);
-            cuda_check(hy_recurrence(false, qq_, kk_, vv_, dec_, nullptr, rec_, states_[run.state_idx], l.heads, l.groups, l.state, l.vdim, r, stream), "state-space recurrence"); MARK(8);
+            cuda_check(hy_recurrence(HY_REC_SCALAR, qq_, kk_, vv_, dec_, nullptr, rec_, states_[run.state_idx], l.heads, l.groups, l.state, l.vdim, r, stream), "state-space recurrence"); MARK(8);
             cuda_check(hy_gated_norm(f32_, rec_, inner, inner / l.norm_groups, w.norm_w, inner, at(proj_, w.off_a), ld_proj_, 1, 1, w.D, l.vdim, conv_, ld_conv_, mix_, ld_mix_,
                                      hc_.eps, T, stream), "gated norm"); MARK(9);
         }

@@ -1,7 +1,9 @@
 // hybrid_model.hpp — device-resident model of the hybrid decoder family (configuration: hybrid_config.hpp, kernels: hybrid_kernels.hpp).
 // It plugs into the same scheduler as the Llama-family DeviceModel: rows of a step arrive as a StepInput (prefill chunks and single decode
 // tokens alike), attention layers keep their compressed keys (latent attention) or their keys and values (windowed attention) in the engine's
-// 64-token pages, recurrent layers keep an fp32 state and their convolution tails in the sequence's state slot.
+// 64-token pages, recurrent layers keep an fp32 state and their convolution tails (or, for a matrix memory, its normaliser and running
+// maximum) in the sequence's state slot.  Designs whose norm follows the sum (x <- norm(alpha x + sublayer(x))) run mixer and feed-forward in
+// sequence; the others run them side by side on norms of the same residual.
 #pragma once
 #include <functional>
 #include <string>
@@ -42,6 +44,13 @@ private:
         int conv_ch = 0;
         float* correction = nullptr; void *gu = nullptr, *down = nullptr; int ffp = 0;       // experts: gu [E][2 ffp][ldw], down [E][W][ffp]
         CUtensorMap tm_gu[2], tm_down[2]; bool moe_tc = false;                               // grouped tensor-core path: BLOCK_N = 128, 256
+        int n_exp = 0, n_top = 0, ff_max = 0;         // experts and choices per token as the kernels see them (a shared expert is one more expert that every token chooses)
+        int32_t* table = nullptr; void* shared_gate = nullptr;                               // router by token id; gate row of the shared expert
+        Mat up, dn;                                   // dense feed-forward
+        // linear attention and attention beside a matrix memory: segments of the fused input projection, second stage and biases
+        int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_a1 = 0, off_lq = 0, off_lk = 0, off_lv = 0;
+        float *a2_bias = nullptr, *decay = nullptr, *o2_bias = nullptr, *out_w1 = nullptr, *out_w2 = nullptr, *gates_bias = nullptr;
+        Mat o2, gates;                                // output projection of the attention side; [W_i ; W_f] of the matrix memory (fp32 out)
     };
     struct RopeTable { float base; int dims; float *cos = nullptr, *sin = nullptr; };
 
@@ -51,9 +60,13 @@ private:
     Mat upload_mat(const HostMat& m);
     HostMat tensor(const std::string& name, int N, int K);                // checkpoint tensor (or seeded values) as fp32 [N, K]; K == 0: any width
     std::vector<float> vec(const std::string& name, int n, float init_mean, float init_spread);
-    void gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha, const void* bias_act = nullptr);
-    void moe(const LayerW& w, const HyLayer& l, const void* h, const HyRows& r, const std::function<void(int)>& mark);
-    int cache_row_width(const HyLayer& l) const { return l.type == HY_WINDOW_ATTENTION ? l.kv_heads * (l.maps * l.dim + l.vdim) : l.kv_rank + l.rot_dim; }
+    void gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha, const void* bias_act = nullptr, int act = 0);
+    // routed experts (and a dense feed-forward): x = beta x + sum of the chosen experts' outputs
+    void moe(const LayerW& w, const HyLayer& l, const void* h, const HyRows& r, const std::function<void(int)>& mark, const int32_t* tokens = nullptr, float beta = 1.f);
+    int rope_table(float base, int dims);
+    void linear_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const std::function<void(int)>& mark);
+    bool has_tensor(const std::string& name) const;
+    int cache_row_width(const HyLayer& l) const { return (l.type == HY_WINDOW_ATTENTION || l.type == HY_ATTENTION_BESIDE_MEMORY) ? l.kv_heads * (l.maps * l.dim + l.vdim) : l.kv_rank + l.rot_dim; }
 
     HybridConfig hc_; bool f32_ = false; size_t es_ = 2;
     struct SafeTensorsHolder; SafeTensorsHolder* st_ = nullptr;
@@ -62,12 +75,15 @@ private:
     void* embed_ = nullptr; Mat head_, loop_in_; float *loop_step_ = nullptr, *final_norm_ = nullptr;
     std::vector<void*> caches_;                    // per attention execution: [num_pages * 64][kv_rank + rot_dim] in the activation type
     std::vector<float*> states_; std::vector<void*> tails_;      // per recurrent execution: [slots][heads * dim * vdim] fp32, [slots][(taps - 1) * channels]
+    std::vector<float*> aux_;                      // per matrix-memory execution: [slots][heads * dim] normaliser, then [slots][heads] running maximum
     int MR_ = 0, MS_ = 0, Wld_ = 0;
     // activations
     float *x_ = nullptr, *x0_ = nullptr, *q_abs_ = nullptr, *qq_ = nullptr, *kk_ = nullptr, *vv_ = nullptr, *dec_ = nullptr, *beta_ = nullptr, *rec_ = nullptr, *wgt_ = nullptr,
           *logits_ = nullptr, *moe_y_ = nullptr, *rlog_ = nullptr;
     void *cat_ = nullptr, *h_ = nullptr, *h2_ = nullptr, *proj_ = nullptr, *p2_ = nullptr, *conv_ = nullptr, *lat_ = nullptr, *mix_ = nullptr, *act_ = nullptr, *hs_ = nullptr, *moe_a_ = nullptr;
-    int ld_proj_ = 0, ld_p2_ = 0, ld_conv_ = 0, ld_mix_ = 0;
+    int ld_proj_ = 0, ld_p2_ = 0, ld_conv_ = 0, ld_mix_ = 0, ld_mix2_ = 0, ld_gates_ = 0;
+    float *y_ = nullptr, *y2_ = nullptr, *gates_ = nullptr, *gin_ = nullptr, *floor_ = nullptr, *mprev_ = nullptr, *ndot_ = nullptr;     // post-norm designs: sublayer outputs; matrix memory: gates and normaliser terms
+    void* mix2_ = nullptr;                         // attention side of a layer with two mixers
     int32_t *idx_ = nullptr, *d_out_ids_ = nullptr, *tile_expert_ = nullptr, *row_src_ = nullptr, *n_tiles_ = nullptr, *dst_of_ = nullptr; int max_tiles_ = 0;
     int32_t* h_meta_buf_[2] = {nullptr, nullptr}; cudaEvent_t meta_ev_[2] = {nullptr, nullptr}; int meta_idx_ = 0;
     int32_t* d_meta_ = nullptr; size_t meta_cap_words_ = 0;

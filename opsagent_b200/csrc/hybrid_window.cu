@@ -5,7 +5,9 @@
 // (2 = differential attention: the head's query and key rows hold [map 1 | map 2], both maps weigh the same values, and the head's output is
 // (a1 - lambda a2) scaled to unit RMS times out_scale); a sliding window of `window` positions plus the first `keep_first` positions of the
 // sequence; an optional RMS norm of every query / key map; an optional sink logit per head that only enlarges the softmax denominator; a
-// sigmoid output gate per channel or per head.  Softmax, norms and gates are fp32 in both element types.
+// sigmoid output gate per channel or per head; optional score modifiers — a soft cap (cap tanh(score / cap)) and a penalty per position of
+// distance with a slope per head — and, in the preparation step, one RMS norm over the whole query / key projection and a query temperature
+// that grows with the logarithm of the position.  Softmax, norms, score modifiers and gates are fp32 in both element types.
 #include "hybrid_common.cuh"
 #include "hybrid_kernels.hpp"
 
@@ -93,6 +95,36 @@ __global__ void __launch_bounds__(128) hy_win_prep_vec8_kernel(HyWinAttn a, __nv
     if (v) for (int c = tid * 8; c < a.kv_heads * a.vdim; c += 128 * 8) *reinterpret_cast<uint4*>(crow + KW + c) = *reinterpret_cast<const uint4*>(v + (long long)t * ldkv + c);
 }
 
+// qk_norm = 2: one RMS norm over the whole q projection of the row (all heads and maps) and one over the whole k projection, weights of
+// those sizes; then the query temperature.  Queries in place, keys and values into the row's cache slot.  One CTA per row.
+__device__ __forceinline__ float win_q_temp(const HyWinAttn& a, int pos) {
+    return a.q_temp_every > 0 ? 1.0f + a.q_temp_coef * logf((float)((pos + 1) / a.q_temp_every) + 1.0f) : 1.0f;
+}
+template <typename TA>
+__global__ void __launch_bounds__(128) hy_win_prep_whole_kernel(HyWinAttn a, TA* __restrict__ q, int ldq, const TA* __restrict__ k, const TA* __restrict__ v, int ldkv,
+                                                                const float* __restrict__ qw, const float* __restrict__ kw, float eps, TA* __restrict__ cache, HyRows r) {
+    HY_PDL();
+    __shared__ float red[32];
+    const long long t = blockIdx.x;
+    const int QW = a.heads * a.maps * a.dim, KW = a.kv_heads * a.maps * a.dim, CW = KW + a.kv_heads * a.vdim;
+    TA* qr = q + t * ldq; TA* crow = cache + (long long)r.slots[t] * CW;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < QW; c += blockDim.x) { const float x = ldf(qr + c); sq = fmaf(x, x, sq); }
+    if (k) for (int c = threadIdx.x; c < KW; c += blockDim.x) { const float x = ldf(k + t * ldkv + c); sk = fmaf(x, x, sk); }
+    const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)QW + eps) * win_q_temp(a, r.positions[t]);
+    const float rk = k ? 1.0f / sqrtf(block_sum(sk, red) / (float)KW + eps) : 0.f;
+    for (int c = threadIdx.x; c < QW; c += blockDim.x) stf(qr + c, ldf(qr + c) * rq * qw[c]);
+    if (k) for (int c = threadIdx.x; c < KW; c += blockDim.x) stf(crow + c, ldf(k + t * ldkv + c) * rk * kw[c]);
+    if (v) for (int c = threadIdx.x; c < a.kv_heads * a.vdim; c += blockDim.x) crow[KW + c] = v[t * ldkv + c];
+}
+
+// score modifiers shared by every form: s is the scaled score of the query at position p (head h) with the key at position j
+__device__ __forceinline__ float win_head_slope(const HyWinAttn& a, int h) { return a.slope_exp > 0.f ? exp2f(-a.slope_exp * (float)(h + 1) / (float)a.heads) : 0.f; }
+__device__ __forceinline__ float win_tanh(float x) {          // 1 - 2 / (e^2x + 1): relative error of a few fp32 ulps from the SFU exponent and a full division
+    const float e = ex2_approx(fminf(x * 2.8853900817779268f, 80.f));
+    return 1.0f - 2.0f / (e + 1.0f);
+}
+
 // The visible keys of a query at position p, in the order every kernel walks them: the kept first positions that the window no longer
 // covers, then the window.  n = count; key(i) = i-th visible position.
 struct WinKeys {
@@ -123,6 +155,7 @@ __global__ void __launch_bounds__(128) hy_win_attention_kernel(HyWinAttn a, cons
     const int seq = r.row_seq[t], pos = r.positions[t];
     const int32_t* bt = r.block_tables + (long long)seq * r.max_pages_per_seq;
     const WinKeys wk(pos, a.window, a.keep_first);
+    const float slope = win_head_slope(a, h);
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, acc[2][WIN_MAXV];
 #pragma unroll
     for (int mp = 0; mp < 2; ++mp)
@@ -141,6 +174,8 @@ __global__ void __launch_bounds__(128) hy_win_attention_kernel(HyWinAttn a, cons
             float d = 0.f;
             for (int c = lane; c < D; c += 32) d = fmaf(qs[mp * D + c], ldf(kr + mp * D + c), d);
             d = warp_sum(d);
+            if (a.softcap > 0.f) d = a.softcap * tanhf(d / a.softcap);
+            d -= slope * (float)(pos - j);
             const float mn = fmaxf(m[mp], d), corr = expf(m[mp] - mn), p = expf(d - mn);
             l[mp] = l[mp] * corr + p; m[mp] = mn;
 #pragma unroll
@@ -205,7 +240,7 @@ __global__ void __launch_bounds__(128) hy_win_attention_kernel(HyWinAttn a, cons
 // output projection's input.
 // ---------------------------------------------------------------------------------------------------------------------------------
 constexpr int WIN_MQ = 64, WIN_KT = 32;
-template <int MAPS, int NVB>
+template <int MAPS, int NVB, bool MOD>      // MOD: soft cap and / or distance slope on the scores
 __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ cache,
                                                                    const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int ldg,
                                                                    __nv_bfloat16* __restrict__ out, int ldo, float eps, HyRows r, const int32_t* __restrict__ tile_seq,
@@ -261,7 +296,10 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
 #pragma unroll
         for (int i = 0; i < NVB; ++i) { o[mp][i][0] = o[mp][i][1] = o[mp][i][2] = o[mp][i][3] = 0.f; }
     }
-    const float qscale = a.scale * 1.4426950408889634f;
+    // MOD: the scores are scaled, capped, given their distance penalty and brought to base-2 units right after the product
+    const float qscale = MOD ? 1.0f : a.scale * 1.4426950408889634f;
+    const float inv_cap = a.softcap > 0.f ? a.scale / a.softcap : 0.f;
+    const float slope_lo = MOD ? win_head_slope(a, g * HG + (q0 + 16 * warp + (lane >> 2)) % HG) : 0.f, slope_hi = MOD ? win_head_slope(a, g * HG + (q0 + 16 * warp + (lane >> 2) + 8) % HG) : 0.f;
     const bool active = 16 * warp < nq;
     const int wp_min = active ? qpos_of(16 * warp) : 0, wp_max = active ? qpos_of(min(16 * warp + 15, nq - 1)) : 0;      // positions of the warp's first and last query slot
     load_tile(0, 0);
@@ -291,6 +329,16 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
                     mma_bf16_16816(s[0], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[1], a0, a1, a2, a3, b2, b3);
                     ldmatrix_x4(ka + 16 * QP * 2 + ks * 32, b0, b1, b2, b3);
                     mma_bf16_16816(s[2], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[3], a0, a1, a2, a3, b2, b3);
+                }
+                if (MOD) {
+#pragma unroll
+                    for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int key = kt * WIN_KT + nb * 8 + (lane & 3) * 2 + (c & 1);
+                            const float v = a.softcap > 0.f ? a.softcap * win_tanh(s[nb][c] * inv_cap) : s[nb][c] * a.scale;
+                            s[nb][c] = (v - (c < 2 ? slope_lo * (float)(p_lo - key) : slope_hi * (float)(p_hi - key))) * 1.4426950408889634f;
+                        }
                 }
                 float mx_lo = -INFINITY, mx_hi = -INFINITY;
                 if (!whole) {                          // a tile on an edge of the mask: per query position
@@ -398,7 +446,7 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
 // query slot join them in warp order and finish the head (sink, a1 - lambda a2, unit RMS, gate).  Which tiles a warp takes depends on the
 // row's position only.
 constexpr int WIN_DEC_WARPS = 8;
-template <int MAPS, int NVB>
+template <int MAPS, int NVB, bool MOD>
 __global__ void __launch_bounds__(256) hy_win_decode_mma_kernel(HyWinAttn a, const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ cache,
                                                                 const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int ldg,
                                                                 __nv_bfloat16* __restrict__ out, int ldo, float eps, HyRows r, const int32_t* __restrict__ tile_seq,
@@ -441,6 +489,8 @@ __global__ void __launch_bounds__(256) hy_win_decode_mma_kernel(HyWinAttn a, con
         for (int i = 0; i < NVB; ++i) { o[mp][i][0] = o[mp][i][1] = o[mp][i][2] = o[mp][i][3] = 0.f; }
     }
     const float qscale = a.scale * 1.4426950408889634f;
+    const float inv_cap = a.softcap > 0.f ? a.scale / a.softcap : 0.f;
+    const float slope_lo = MOD ? win_head_slope(a, g * HG + (q0 + (lane >> 2)) % HG) : 0.f, slope_hi = MOD ? win_head_slope(a, g * HG + (q0 + (lane >> 2) + 8) % HG) : 0.f;
     const int p_lo = qpos[lane >> 2], p_hi = qpos[(lane >> 2) + 8];
     const int kc = QD / 8, nc = kc + VD / 8, step_j = 32 / nc, step_c = 32 % nc, j0 = lane / nc, c0 = lane % nc;      // a lane walks its warp's tile chunks in steps of 32
     for (int it = warp; it < n_it; it += WIN_DEC_WARPS) {
@@ -484,6 +534,10 @@ __global__ void __launch_bounds__(256) hy_win_decode_mma_kernel(HyWinAttn a, con
                 for (int c = 0; c < 4; ++c) {
                     const int key = kt * WIN_KT + nb * 8 + (lane & 3) * 2 + (c & 1), p = c < 2 ? p_lo : p_hi;
                     const bool vis = key <= p && (p - key < a.window || key < a.keep_first);
+                    if (MOD) {
+                        const float v = a.softcap > 0.f ? a.softcap * win_tanh(s[nb][c] * inv_cap) : s[nb][c] * a.scale;
+                        s[nb][c] = vis ? (v - (c < 2 ? slope_lo : slope_hi) * (float)(p - key)) * 1.4426950408889634f : -INFINITY;
+                    } else
                     s[nb][c] = vis ? s[nb][c] * qscale : -INFINITY;
                     if (c < 2) mx_lo = fmaxf(mx_lo, s[nb][c]); else mx_hi = fmaxf(mx_hi, s[nb][c]);
                 }
@@ -594,8 +648,12 @@ cudaError_t hy_rmsnorm_pair(bool f32, const float* x, const int32_t* rows, const
 
 cudaError_t hy_win_prep(bool f32, const HyWinAttn& a, void* q, int ldq, const void* k, const void* v, int ldkv, const float* q_norm_w, const float* k_norm_w, float eps, void* cache,
                         const HyRows& r, cudaStream_t s) {
-    if (r.T <= 0 || (!a.qk_norm && !k)) return cudaSuccess;
+    if (r.T <= 0 || (!a.qk_norm && !k && a.q_temp_every <= 0)) return cudaSuccess;
     using bf = __nv_bfloat16;
+    if (a.qk_norm == 2)
+        return f32 ? launch_plain(hy_win_prep_whole_kernel<float>, dim3(r.T), dim3(128), 0, s, a, (float*)q, ldq, (const float*)k, (const float*)v, ldkv, q_norm_w, k_norm_w, eps, (float*)cache, r)
+                   : launch_plain(hy_win_prep_whole_kernel<bf>, dim3(r.T), dim3(128), 0, s, a, (bf*)q, ldq, (const bf*)k, (const bf*)v, ldkv, q_norm_w, k_norm_w, eps, (bf*)cache, r);
+    if (a.q_temp_every > 0) return cudaErrorInvalidValue;      // the query temperature is applied by the whole-projection form only
     const int gs = a.dim / 8;
     const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(cache) |
                            reinterpret_cast<uintptr_t>(q_norm_w) | reinterpret_cast<uintptr_t>(k_norm_w)) & 15) == 0;
@@ -627,11 +685,12 @@ cudaError_t hy_win_attention(bool f32, const HyWinAttn& a, const void* q, int ld
                               eps, r);
 }
 
+static bool win_modded(const HyWinAttn& a) { return a.softcap > 0.f || a.slope_exp > 0.f; }
 bool hy_win_mma_supported(const HyWinAttn& a) {
     const bool vd_ok = a.vdim == 16 || a.vdim == 32 || a.vdim == 64 || a.vdim == 96 || a.vdim == 128;
-    return hy_win_supported(a) && a.dim % 16 == 0 && a.dim <= 128 && vd_ok;
+    return hy_win_supported(a) && a.dim % 16 == 0 && a.dim <= 128 && vd_ok && !(win_modded(a) && a.maps != 1);      // score modifiers on the tensor cores: one map
 }
-template <int MAPS, int NVB>
+template <int MAPS, int NVB, bool MOD>
 static cudaError_t win_mma_launch(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
                                   const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
     using bf = __nv_bfloat16;
@@ -639,14 +698,14 @@ static cudaError_t win_mma_launch(const HyWinAttn& a, const void* q, int ldq, co
     const size_t smem = (size_t)(WIN_MQ * QP + 2 * WIN_KT * QP + 2 * WIN_KT * VP) * 2 + WIN_MQ * 4;
     static size_t raised = 0;          // per instantiation
     if (smem > 48 * 1024 && smem > raised) {
-        cudaError_t e = cudaFuncSetAttribute(hy_win_attention_mma_kernel<MAPS, NVB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(hy_win_attention_mma_kernel<MAPS, NVB, MOD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         raised = smem;
     }
-    return launch_plain(hy_win_attention_mma_kernel<MAPS, NVB>, dim3(n_tiles, a.kv_heads), dim3(128), smem, s, a, (const bf*)q, ldq, (const bf*)cache, sink, (const bf*)gate, ldg,
+    return launch_plain(hy_win_attention_mma_kernel<MAPS, NVB, MOD>, dim3(n_tiles, a.kv_heads), dim3(128), smem, s, a, (const bf*)q, ldq, (const bf*)cache, sink, (const bf*)gate, ldg,
                         (bf*)out, ldo, eps, r, tile_seq, tile_q0);
 }
-template <int MAPS, int NVB>
+template <int MAPS, int NVB, bool MOD>
 static cudaError_t win_decode_launch(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
                                      const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
     using bf = __nv_bfloat16;
@@ -655,31 +714,37 @@ static cudaError_t win_decode_launch(const HyWinAttn& a, const void* q, int ldq,
     const size_t smem = (size_t)16 * QP * 2 + (tiles > parts ? tiles : parts);
     static size_t raised = 0;
     if (smem > 48 * 1024 && smem > raised) {
-        cudaError_t e = cudaFuncSetAttribute(hy_win_decode_mma_kernel<MAPS, NVB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(hy_win_decode_mma_kernel<MAPS, NVB, MOD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         raised = smem;
     }
-    return launch_plain(hy_win_decode_mma_kernel<MAPS, NVB>, dim3(n_tiles, a.kv_heads), dim3(256), smem, s, a, (const bf*)q, ldq, (const bf*)cache, sink, (const bf*)gate, ldg,
+    return launch_plain(hy_win_decode_mma_kernel<MAPS, NVB, MOD>, dim3(n_tiles, a.kv_heads), dim3(256), smem, s, a, (const bf*)q, ldq, (const bf*)cache, sink, (const bf*)gate, ldg,
                         (bf*)out, ldo, eps, r, tile_seq, tile_q0);
 }
 cudaError_t hy_win_attention_mma(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
                                  const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
     if (n_tiles <= 0) return cudaSuccess;
     if (!hy_win_mma_supported(a)) return cudaErrorInvalidValue;
-#define WIN_CASE(M, N) if (a.maps == M && a.vdim == N * 8) return win_mma_launch<M, N>(a, q, ldq, cache, sink, gate, ldg, out, ldo, eps, r, tile_seq, tile_q0, n_tiles, s)
+#define WIN_CASE(M, N) if (a.maps == M && a.vdim == N * 8) return win_mma_launch<M, N, false>(a, q, ldq, cache, sink, gate, ldg, out, ldo, eps, r, tile_seq, tile_q0, n_tiles, s)
+#define WIN_CASE_MOD(N) if (a.vdim == N * 8) return win_mma_launch<1, N, true>(a, q, ldq, cache, sink, gate, ldg, out, ldo, eps, r, tile_seq, tile_q0, n_tiles, s)
+    if (win_modded(a)) { WIN_CASE_MOD(2); WIN_CASE_MOD(4); WIN_CASE_MOD(8); WIN_CASE_MOD(12); WIN_CASE_MOD(16); return cudaErrorInvalidValue; }
     WIN_CASE(1, 2); WIN_CASE(1, 4); WIN_CASE(1, 8); WIN_CASE(1, 12); WIN_CASE(1, 16);
     WIN_CASE(2, 2); WIN_CASE(2, 4); WIN_CASE(2, 8); WIN_CASE(2, 12); WIN_CASE(2, 16);
 #undef WIN_CASE
+#undef WIN_CASE_MOD
     return cudaErrorInvalidValue;
 }
 cudaError_t hy_win_decode_mma(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
                               const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
     if (n_tiles <= 0) return cudaSuccess;
     if (!hy_win_mma_supported(a)) return cudaErrorInvalidValue;
-#define WIN_CASE(M, N) if (a.maps == M && a.vdim == N * 8) return win_decode_launch<M, N>(a, q, ldq, cache, sink, gate, ldg, out, ldo, eps, r, tile_seq, tile_q0, n_tiles, s)
+#define WIN_CASE(M, N) if (a.maps == M && a.vdim == N * 8) return win_decode_launch<M, N, false>(a, q, ldq, cache, sink, gate, ldg, out, ldo, eps, r, tile_seq, tile_q0, n_tiles, s)
+#define WIN_CASE_MOD(N) if (a.vdim == N * 8) return win_decode_launch<1, N, true>(a, q, ldq, cache, sink, gate, ldg, out, ldo, eps, r, tile_seq, tile_q0, n_tiles, s)
+    if (win_modded(a)) { WIN_CASE_MOD(2); WIN_CASE_MOD(4); WIN_CASE_MOD(8); WIN_CASE_MOD(12); WIN_CASE_MOD(16); return cudaErrorInvalidValue; }
     WIN_CASE(1, 2); WIN_CASE(1, 4); WIN_CASE(1, 8); WIN_CASE(1, 12); WIN_CASE(1, 16);
     WIN_CASE(2, 2); WIN_CASE(2, 4); WIN_CASE(2, 8); WIN_CASE(2, 12); WIN_CASE(2, 16);
 #undef WIN_CASE
+#undef WIN_CASE_MOD
     return cudaErrorInvalidValue;
 }
 
