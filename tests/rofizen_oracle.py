@@ -245,7 +245,7 @@ def random_weights(cfg, seed, spread=1.0):
     w = {}
     for name, shape in tensor_shapes(cfg).items():
         if name.endswith(".table"):
-            E = [l for l in cfg["layers"] if l.get("mlp") and l["mlp"]["kind"] == "moe"][0]["mlp"]["router"]["experts"]
+            E = cfg["layers"][int(name[1:name.index(".")])]["mlp"]["router"]["experts"]
             w[name] = np.stack([rng.permutation(E)[: shape[1]] for _ in range(shape[0])]).astype(np.int32)
         elif len(shape) == 1:
             is_norm = name.endswith("norm") or name.endswith("norm1") or name.endswith("norm2") or name.endswith(".out")
@@ -280,3 +280,50 @@ def write_checkpoint(folder, cfg, w):
     hj += b" " * (-len(hj) % 8)
     with open(os.path.join(folder, "model.safetensors"), "wb") as f:
         f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+
+
+# ---- configurations for the tests ---------------------------------------------------------------------------------------------------------
+
+def rel_err(got, want):
+    """per row: RMS over the vocabulary of the difference (its mean taken off), relative to the spread of the expected logits"""
+    d = got - want
+    d = d - d.mean(-1, keepdims=True)
+    return np.sqrt((d * d).mean(-1)) / want.std()
+
+
+def dense(ff=40):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe(experts=6, top=2, ff=24, shared_ff=40):
+    m = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared_ff:
+        m["shared"] = {"ff": shared_ff}
+    return m
+
+
+def gla_layer(heads=3, dim=8, vdim=12, tau=4.0, rank=5, mlp=None):
+    return {"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau, "_rank": rank}, "mlp": mlp}
+
+
+def retention_layer(heads=3, dim=12, vdim=8, decay=None, rot_dims=8, rot_base=500.0, mlp=None):
+    decay = decay or [1.0 - 2.0 ** (-3 - i) for i in range(heads)]
+    return {"type": "retention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay, "rot": {"base": rot_base, "dims": rot_dims}}, "mlp": mlp}
+
+
+def parallel_layer(heads=4, kv_heads=2, dim=8, vdim=12, scale=0.4, softcap=6.0, coef=0.5, every=5, r_heads=3, r_dim=12, r_vdim=8, gate_cap=7.0, mlp=None):
+    return {"type": "parallel", "mlp": mlp,
+            "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "softcap": softcap, "q_temp": {"coef": coef, "every": every}},
+                      "right": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "gate_cap": gate_cap}}}
+
+
+def make_config(layers, width=40, vocab=77, embed_scale=3.0, alpha=1.7, eps=1e-5):
+    return {"architecture": "Rofizen", "embedding": {"scale": embed_scale}, "layers": layers, "norm": {"eps": eps}, "postln_alpha": alpha, "vocab": vocab, "width": width}
+
+
+def sharpen(w, factor):
+    """queries that single out keys: the attention side's query norm weights and the matrix memory's input-gate rows grow by `factor`"""
+    for name in w:
+        if name.endswith("left.q.norm") or name.endswith("right.i"):
+            w[name] = bf16_round(w[name] * factor)
+    return w
