@@ -147,9 +147,8 @@ cudaError_t hy_lin_prep(bool f32, const HyLinPrep& p, const void* q, const void*
                         const float* decay_head, float* dec_head, const float* rope_cos, const float* rope_sin, const HyRows& r, cudaStream_t s);
 // Matrix memory.  gates [T, ldg] fp32 = [W_i h + b_i | W_f h + b_f] (heads each).  hy_mlstm_gates: log gates i = cap tanh(. / cap),
 // f = logsigmoid(cap tanh(. / cap)); the running maximum m_t = max(f_t + m_(t-1), i_t) per (sequence, head), carried in mstate [slots, heads]
-// (a sequence whose step starts at position 0 starts from m = 0); out: dec[t, h] = exp(f + m_(t-1) - m_t), gin[t, h] = exp(i - m_t), floor_[t, h] = exp(-m_t);
-// mprev [T, heads]: scratch
-cudaError_t hy_mlstm_gates(const float* gates, int ldg, int heads, float cap, float* mstate, float* dec, float* gin, float* floor_, float* mprev, const HyRows& r, cudaStream_t s);
+// (a sequence whose step starts at position 0 starts from m = 0); out: dec[t, h] = exp(f + m_(t-1) - m_t), gin[t, h] = exp(i - m_t), floor_[t, h] = exp(-m_t)
+cudaError_t hy_mlstm_gates(const float* gates, int ldg, int heads, float cap, float* mstate, float* dec, float* gin, float* floor_, const HyRows& r, cudaStream_t s);
 // qq = q dim^-1/2, kk = gin * k, vv = v
 cudaError_t hy_mlstm_prep(bool f32, int heads, int dim, int vdim, const void* q, const void* k, const void* v, int ld, const float* gin, float* qq, float* kk, float* vv, int T, cudaStream_t s);
 // group-wise RMS norm with a gate: v = o (+ skip[c / skip_block] * xs[t, c]); gate_before ? v *= act(gate) : -; v /= rms over each group of

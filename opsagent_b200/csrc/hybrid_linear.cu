@@ -80,40 +80,46 @@ __global__ void __launch_bounds__(128) hy_lin_prep_kernel(HyLinPrep p, const TA*
     if (dec_head) for (int i = threadIdx.x; i < H; i += blockDim.x) dec_head[t * H + i] = decay_head[i];
 }
 
-// log gates of every (row, head): gin <- i = cap tanh(z_i / cap), dec <- f = logsigmoid(cap tanh(z_f / cap))
-__global__ void hy_mlstm_loggates_kernel(const float* __restrict__ gates, int ldg, int H, float cap, float* __restrict__ dec, float* __restrict__ gin, long long n) {
+// Gates of the matrix memory, one CTA per (sequence, head).  Every thread owns a run of consecutive rows.  Pass 1: log gates
+// i = cap tanh(z_i / cap), f = logsigmoid(cap tanh(z_f / cap)) and the run's effect on the running maximum as a pair (A, B): m_out =
+// max(m_in + A, B) with A = sum of f and B = the maximum reached from minus infinity (the update m <- max(m + f, i) composes that way).
+// One thread chains the runs' pairs from the carried maximum; pass 2 walks each run again from its incoming maximum and writes
+// dec = exp(f + m_(t-1) - m_t), gin = exp(i - m_t), floor_ = exp(-m_t).  The last row of a run takes the chained value as its maximum, so
+// that the next run starts from exactly the number this one ended with: the maximum is only a stabiliser (state, normaliser and floor
+// all carry exp(-m_t)), what matters is that every row divides by the same number the next row multiplies with.
+constexpr int MLSTM_SCAN_THREADS = 128;
+__global__ void __launch_bounds__(MLSTM_SCAN_THREADS) hy_mlstm_gates_kernel(const float* __restrict__ gates, int ldg, int H, float cap, float* __restrict__ mstate,
+                                                                            float* __restrict__ dec, float* __restrict__ gin, float* __restrict__ floor_, HyRows r) {
     HY_PDL();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const long long t = i / H; const int h = (int)(i % H);
-    gin[i] = cap * tanhf(gates[t * ldg + h] / cap);
-    dec[i] = log_sigmoidf_(cap * tanhf(gates[t * ldg + H + h] / cap));
-}
-// one thread per (sequence, head) walks the sequence's rows: m_t = max(f_t + m_(t-1), i_t); floor_ <- m_t, mprev <- m_(t-1)
-__global__ void hy_mlstm_scan_kernel(const float* __restrict__ dec, const float* __restrict__ gin, int H, float* __restrict__ mstate, float* __restrict__ floor_,
-                                     float* __restrict__ mprev, HyRows r) {
-    HY_PDL();
-    const int seq = blockIdx.x;
+    __shared__ float sA[MLSTM_SCAN_THREADS], sB[MLSTM_SCAN_THREADS], sM[MLSTM_SCAN_THREADS + 1];
+    const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq];
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        float* ms = mstate + (long long)r.seq_state[seq] * H + h;
-        float m = pos0 > 0 ? *ms : 0.f;
-        for (int i = 0; i < len; ++i) {
-            const long long at = (long long)(row0 + i) * H + h;
-            mprev[at] = m;
-            m = fmaxf(dec[at] + m, gin[at]);
-            floor_[at] = m;
-        }
-        *ms = m;
+    const int per = (len + MLSTM_SCAN_THREADS - 1) / MLSTM_SCAN_THREADS, t0 = min(len, tid * per), t1 = min(len, t0 + per);
+    const float inv_cap = 1.0f / cap;
+    float A = 0.f, B = -INFINITY;
+    for (int t = t0; t < t1; ++t) {
+        const long long row = row0 + t;
+        const float i = cap * tanhf(gates[row * ldg + h] * inv_cap), f = log_sigmoidf_(cap * tanhf(gates[row * ldg + H + h] * inv_cap));
+        gin[row * H + h] = i; dec[row * H + h] = f;
+        A += f; B = fmaxf(B + f, i);
     }
-}
-// dec <- exp(f + m_(t-1) - m_t), gin <- exp(i - m_t), floor_ <- exp(-m_t)
-__global__ void hy_mlstm_weights_kernel(float* __restrict__ dec, float* __restrict__ gin, float* __restrict__ floor_, const float* __restrict__ mprev, long long n) {
-    HY_PDL();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const float m = floor_[i];
-    dec[i] = expf(dec[i] + mprev[i] - m); gin[i] = expf(gin[i] - m); floor_[i] = expf(-m);
+    sA[tid] = A; sB[tid] = B;
+    __syncthreads();
+    if (tid == 0) {
+        float* ms = mstate + (long long)r.seq_state[seq] * H + h;
+        float m = pos0 > 0 ? *ms : 0.f;                    // a sequence that starts in this step starts from 0
+        for (int j = 0; j < MLSTM_SCAN_THREADS; ++j) { sM[j] = m; m = fmaxf(m + sA[j], sB[j]); }
+        sM[MLSTM_SCAN_THREADS] = m; *ms = m;
+    }
+    __syncthreads();
+    float m = sM[tid];
+    for (int t = t0; t < t1; ++t) {
+        const long long at = (long long)(row0 + t) * H + h;
+        const float f = dec[at], i = gin[at];
+        const float mn = t == t1 - 1 ? sM[tid + 1] : fmaxf(f + m, i);
+        dec[at] = expf(f + m - mn); gin[at] = expf(i - mn); floor_[at] = expf(-mn);
+        m = mn;
+    }
 }
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_mlstm_prep_kernel(int H, int D, int VD, const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, int ld,
@@ -167,14 +173,9 @@ cudaError_t hy_lin_prep(bool f32, const HyLinPrep& p, const void* q, const void*
                               dec_head, rope_cos, rope_sin, r);
 }
 
-cudaError_t hy_mlstm_gates(const float* gates, int ldg, int heads, float cap, float* mstate, float* dec, float* gin, float* floor_, float* mprev, const HyRows& r, cudaStream_t s) {
+cudaError_t hy_mlstm_gates(const float* gates, int ldg, int heads, float cap, float* mstate, float* dec, float* gin, float* floor_, const HyRows& r, cudaStream_t s) {
     if (r.T <= 0) return cudaSuccess;
-    const long long n = (long long)r.T * heads;
-    cudaError_t e = launch_plain(hy_mlstm_loggates_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, gates, ldg, heads, cap, dec, gin, n);
-    if (e != cudaSuccess) return e;
-    e = launch_plain(hy_mlstm_scan_kernel, dim3(r.S), dim3(32 * ((heads + 31) / 32 > 8 ? 8 : (heads + 31) / 32)), 0, s, (const float*)dec, (const float*)gin, heads, mstate, floor_, mprev, r);
-    if (e != cudaSuccess) return e;
-    return launch_plain(hy_mlstm_weights_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, dec, gin, floor_, (const float*)mprev, n);
+    return launch_plain(hy_mlstm_gates_kernel, dim3(r.S, heads), dim3(MLSTM_SCAN_THREADS), 0, s, gates, ldg, heads, cap, mstate, dec, gin, floor_, r);
 }
 
 cudaError_t hy_mlstm_prep(bool f32, int heads, int dim, int vdim, const void* q, const void* k, const void* v, int ld, const float* gin, float* qq, float* kk, float* vv, int T,

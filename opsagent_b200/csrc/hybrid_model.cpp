@@ -390,7 +390,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     if (max_mix2 > 0) { ld_mix2_ = up8(max_mix2); mix2_ = dmalloc(MR * ld_mix2_ * es_); }
     if (max_gates > 0) {
         ld_gates_ = max_gates; gates_ = (float*)dmalloc(MR * ld_gates_ * 4);
-        gin_ = (float*)dmalloc(MR * max_h * 4); floor_ = (float*)dmalloc(MR * max_h * 4); mprev_ = (float*)dmalloc(MR * max_h * 4); ndot_ = (float*)dmalloc(MR * max_h * 4);
+        gin_ = (float*)dmalloc(MR * max_h * 4); floor_ = (float*)dmalloc(MR * max_h * 4); ndot_ = (float*)dmalloc(MR * max_h * 4);
     }
     hs_ = dmalloc((size_t)MS_ * Wld_ * es_); d_out_ids_ = (int32_t*)dmalloc((size_t)MS_ * 4);
     logits_ = (float*)dmalloc((size_t)opt.max_batch * V * 4);      // own logits: sampling steps only (one row per sequence)
@@ -552,7 +552,7 @@ void HybridModel::linear_mixer(const HyRun& run, const HyLayer& l, const LayerW&
     } else {
         float* aux = aux_[run.state_idx];
         gemm(HY_STORE_F32, h_, Wld_, w.gates, gates_, ld_gates_, T, w.gates_bias, 1.f);
-        cuda_check(hy_mlstm_gates(gates_, ld_gates_, H, n.gate_cap, aux + (size_t)state_slots * H * D, dec_, gin_, floor_, mprev_, r, stream), "matrix memory gates"); MARK(29);
+        cuda_check(hy_mlstm_gates(gates_, ld_gates_, H, n.gate_cap, aux + (size_t)state_slots * H * D, dec_, gin_, floor_, r, stream), "matrix memory gates"); MARK(29);
         cuda_check(hy_mlstm_prep(f32_, H, D, VD, q, k, v, ld_proj_, gin_, qq_, kk_, vv_, T, stream), "matrix memory operands"); MARK(28);
         cuda_check(hy_recurrence(HY_REC_SCALAR, qq_, kk_, vv_, dec_, nullptr, rec_, st, H, H, D, VD, r, stream, aux, ndot_), "matrix memory"); MARK(8);
         cuda_check(hy_gated_norm(f32_, rec_, H * VD, VD, w.norm_w, H * VD, g, ld_proj_, 0, n.gate_silu, nullptr, 1, nullptr, 0, mix_, ld_mix_, hc_.eps, T, stream, ndot_, floor_), "gated norm"); MARK(9);

@@ -82,7 +82,7 @@ private:
           *logits_ = nullptr, *moe_y_ = nullptr, *rlog_ = nullptr;
     void *cat_ = nullptr, *h_ = nullptr, *h2_ = nullptr, *proj_ = nullptr, *p2_ = nullptr, *conv_ = nullptr, *lat_ = nullptr, *mix_ = nullptr, *act_ = nullptr, *hs_ = nullptr, *moe_a_ = nullptr;
     int ld_proj_ = 0, ld_p2_ = 0, ld_conv_ = 0, ld_mix_ = 0, ld_mix2_ = 0, ld_gates_ = 0;
-    float *y_ = nullptr, *y2_ = nullptr, *gates_ = nullptr, *gin_ = nullptr, *floor_ = nullptr, *mprev_ = nullptr, *ndot_ = nullptr;     // post-norm designs: sublayer outputs; matrix memory: gates and normaliser terms
+    float *y_ = nullptr, *y2_ = nullptr, *gates_ = nullptr, *gin_ = nullptr, *floor_ = nullptr, *ndot_ = nullptr;     // post-norm designs: sublayer outputs; matrix memory: gates and normaliser terms
     void* mix2_ = nullptr;                         // attention side of a layer with two mixers
     int32_t *idx_ = nullptr, *d_out_ids_ = nullptr, *tile_expert_ = nullptr, *row_src_ = nullptr, *n_tiles_ = nullptr, *dst_of_ = nullptr; int max_tiles_ = 0;
     int32_t* h_meta_buf_[2] = {nullptr, nullptr}; cudaEvent_t meta_ev_[2] = {nullptr, nullptr}; int meta_idx_ = 0;

@@ -1,6 +1,6 @@
-"""Throughput of the hybrid family beside the closest existing models (`bench.py --arch ratasun | zurevik`): Ratasun beside the Llama-family
-model of equal width, depth and active feed-forward size; Zurevik beside the Ratasun model of equal width, depth and experts (the closest
-design: the same parallel-residual layers with routed experts) and beside that Llama-family model.  Random weights (seeded on load), synthetic token ids; prefill = real chunked prefill of batch x (ctx-1) tokens,
+"""Throughput of the hybrid family beside the closest existing models (`bench.py --arch ratasun | zurevik | rofizen`): Ratasun beside the
+Llama-family model of equal width, depth and active feed-forward size; Zurevik and Rofizen beside the Ratasun model of equal width, depth and
+experts (the closest design: routed experts in every layer; recurrent mixers with an fp32 state like Rofizen's) and beside that Llama-family model.  Random weights (seeded on load), synthetic token ids; prefill = real chunked prefill of batch x (ctx-1) tokens,
 decode = steps of the whole batch, both timed with CUDA events inside the engine (oa_bench_decode).  With --breakdown the per-kernel-class
 device times come from the engine's in-situ event timing (OA_PROFILE_ALL), one pass for prefill and one for decode."""
 from __future__ import annotations
@@ -49,6 +49,25 @@ def zurevik_sizes(name: str) -> dict:
             "layers": [{"type": t, "mixer": m, "mlp": moe} for t, m in order]}
 
 
+def rofizen_sizes(name: str) -> dict:
+    """Rofizen at the width, depth (6 layers) and active feed-forward size of sizes(name): gated linear attention, retention, attention beside a
+    matrix memory, twice; the first layer's feed-forward is dense, the others choose 3 experts by table and add a gated shared expert."""
+    if name == "small":
+        heads, dim, vdim, width, ff, experts = 8, 64, 128, 1024, 512, 16
+        left = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64, "scale": 64 ** -0.5}
+    else:
+        heads, dim, vdim, width, ff, experts = 16, 128, 128, 2048, 1024, 32
+        left = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+    left.update(softcap=30.0, q_temp={"coef": 0.1, "every": 256})
+    gla = {"heads": heads, "dim": dim, "vdim": vdim, "tau": 16.0}
+    ret = {"heads": heads, "dim": dim, "vdim": vdim, "decay": [1.0 - 2.0 ** (-5 - 5 * h / heads) for h in range(heads)], "rot": {"base": 10000.0, "dims": dim}}
+    par = {"left": left, "right": {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": 15.0}}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": 3}, "shared": {"ff": ff}}
+    order = [("gla", gla, {"kind": "dense", "ff": 4 * ff}), ("retention", ret, moe), ("parallel", par, moe), ("gla", gla, moe), ("retention", ret, moe), ("parallel", par, moe)]
+    return {"architecture": "Rofizen", "width": width, "vocab": 32000, "norm": {"eps": 1e-5}, "embedding": {"scale": width ** 0.5}, "postln_alpha": 2.0,
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in order]}
+
+
 def one(engine_cfg: dict, batch: int, ctx: int, steps: int, warmup: int, breakdown: bool) -> dict:
     from .engine import Engine
     out = {}
@@ -74,8 +93,8 @@ def one(engine_cfg: dict, batch: int, ctx: int, steps: int, warmup: int, breakdo
 
 
 def run(args) -> None:
-    zu = args.arch == "zurevik"
-    res = {"metric": "zurevik_vs_ratasun_and_llama_throughput" if zu else "hybrid_vs_llama_throughput", "unit": "tokens/s", "data": "synthetic", "dtype": "bf16", "cases": []}
+    zu = args.arch in ("zurevik", "rofizen")
+    res = {"metric": args.arch + "_vs_ratasun_and_llama_throughput" if zu else "hybrid_vs_llama_throughput", "unit": "tokens/s", "data": "synthetic", "dtype": "bf16", "cases": []}
     for name in args.arch_sizes.split(","):
         sz = sizes(name)
         batch, ctx = args.arch_batch, args.arch_ctx
@@ -89,10 +108,10 @@ def run(args) -> None:
                 return one(dict(common, model_dir=d, **json.loads(args.engine_extra)), batch, ctx, args.steps, args.warmup, args.breakdown)
         case = {"size": name, "batch": batch, "ctx": ctx, "layer_runs": sz["runs"]}
         if zu:
-            case["zurevik"] = folder_model(zurevik_sizes(name))
+            case[args.arch] = folder_model(zurevik_sizes(name) if args.arch == "zurevik" else rofizen_sizes(name))
         case["ratasun"] = hy = folder_model(sz["hybrid"])
         case["llama_equal_size"] = ll = one(dict(common, **sz["llama"]), batch, ctx, args.steps, args.warmup, args.breakdown)
-        new = case["zurevik"] if zu else hy
+        new = case[args.arch] if zu else hy
         case["prefill_ratio"], case["decode_ratio"] = new["prefill_tok_s"] / ll["prefill_tok_s"], new["decode_tok_s"] / ll["decode_tok_s"]
         if zu:
             case["prefill_ratio_to_ratasun"], case["decode_ratio_to_ratasun"] = new["prefill_tok_s"] / hy["prefill_tok_s"], new["decode_tok_s"] / hy["decode_tok_s"]
