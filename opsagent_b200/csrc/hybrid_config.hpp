@@ -192,11 +192,11 @@ struct HybridConfig {
                 l.type = HY_ATTENTION_BESIDE_MEMORY;
                 const Json& a = obj(m, "left", "parallel"); const Json& b = obj(m, "right", "parallel");
                 l.heads = integer(a, "heads", "left"); l.kv_heads = integer(a, "kv_heads", "left"); l.dim = integer(a, "dim", "left"); l.vdim = integer(a, "vdim", "left");
-                l.scale = (float)num(a, "scale", "left"); l.softcap = (float)num(a, "softcap", "left"); l.slope_exp = 8.f;
-                const Json& qt = obj(a, "q_temp", "left");
-                l.q_temp_coef = (float)num(qt, "coef", "q_temp"); l.q_temp_every = integer(qt, "every", "q_temp");
+                l.scale = (float)num(a, "scale", "left"); l.slope_exp = 8.f;
+                if (a.get("softcap") && a.get("softcap")->t == Json::Num) l.softcap = (float)num(a, "softcap", "left");          // absent or 0: scores are not capped
+                if (const Json* qt = a.get("q_temp")) if (qt->t == Json::Obj) { l.q_temp_coef = (float)num(*qt, "coef", "q_temp"); l.q_temp_every = integer(*qt, "every", "q_temp"); if (l.q_temp_every < 1) throw std::runtime_error("config.json: q_temp.every must be at least 1"); }
                 l.window = 1 << 30; l.qk_norm = 2; l.bias = 1; l.out_bias = 1;
-                if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.vdim > 256 || l.dim > 1024 || l.q_temp_every < 1 || !(l.softcap > 0.f)) throw std::runtime_error("config.json: bad attention sizes");
+                if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.vdim > 256 || l.dim > 1024 || l.softcap < 0.f) throw std::runtime_error("config.json: bad attention sizes");
                 HyLinear& n = l.lin;
                 n.kind = HY_LIN_MATRIX_MEMORY; n.heads = integer(b, "heads", "right"); n.dim = integer(b, "dim", "right"); n.vdim = integer(b, "vdim", "right");
                 n.gate_cap = (float)num(b, "gate_cap", "right"); n.norm = HY_LIN_NORM_ALL_WEIGHT; n.gate_silu = 0;

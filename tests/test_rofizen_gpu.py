@@ -74,7 +74,7 @@ SINGLE = {
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(SINGLE))
 def test_each_mechanism_alone(tmp_path, name, dtype):
-    cfg = R.make_config(SINGLE[name], width=36 if "off_every" in name or "odd" in name else 40)
+    cfg = R.make_config(SINGLE[name], width=38 if "off_every" in name else 36 if "odd" in name else 40)
     W = checkpoint(tmp_path, cfg, seed=len(name))
     toks = tokens_of(cfg, 70, 1)                       # crosses a page border
     want = R.forward(cfg, W, toks)

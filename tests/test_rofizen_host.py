@@ -62,7 +62,7 @@ def drop(path):
     mutate(["layers", 0, "type"], "serial"),
     mutate(["layers", 0, "mixer", "left", "kv_heads"], 3),             # does not divide heads
     mutate(["layers", 0, "mixer", "left", "vdim"], 300),               # beyond what the kernels hold
-    mutate(["layers", 0, "mixer", "left", "softcap"], 0.0),
+    mutate(["layers", 0, "mixer", "left", "softcap"], -2.0),
     mutate(["layers", 0, "mixer", "left", "q_temp", "every"], 0),
     mutate(["layers", 0, "mixer", "right", "gate_cap"], -1.0),
     mutate(["layers", 1, "mixer", "tau"], 0.0),
