@@ -118,6 +118,39 @@ __global__ void __launch_bounds__(128) hy_win_prep_whole_kernel(HyWinAttn a, TA*
     if (v) for (int c = threadIdx.x; c < a.kv_heads * a.vdim; c += blockDim.x) crow[KW + c] = v[t * ldkv + c];
 }
 
+// The same for bf16 rows whose projections come in aligned groups of 8 channels: 16 bytes per access, the second pass re-reads what the first
+// left in L1.  Sums run per thread over its own vectors and then over the block: the norm's rounding differs from the kernel above in the
+// last fp32 bits only; a model takes one of the two for all of its steps.
+__global__ void __launch_bounds__(128) hy_win_prep_whole_vec8_kernel(HyWinAttn a, __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k,
+                                                                     const __nv_bfloat16* __restrict__ v, int ldkv, const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                                                     __nv_bfloat16* __restrict__ cache, HyRows r) {
+    HY_PDL();
+    __shared__ float red[32];
+    const long long t = blockIdx.x;
+    const int QW = a.heads * a.maps * a.dim, KW = a.kv_heads * a.maps * a.dim, VW = a.kv_heads * a.vdim, CW = KW + VW;
+    __nv_bfloat16* qr = q + t * ldq; __nv_bfloat16* crow = cache + (long long)r.slots[t] * CW;
+    auto sq8 = [](const uint4& u) {
+        const float x[8] = {bf16lo(u.x), bf16hi(u.x), bf16lo(u.y), bf16hi(u.y), bf16lo(u.z), bf16hi(u.z), bf16lo(u.w), bf16hi(u.w)};
+        float s = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s = fmaf(x[e], x[e], s);
+        return s;
+    };
+    auto scale8 = [](const uint4& u, float rr, const float* w) {
+        const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
+        return make_uint4(pack_bf16x2(bf16lo(u.x) * rr * w0.x, bf16hi(u.x) * rr * w0.y), pack_bf16x2(bf16lo(u.y) * rr * w0.z, bf16hi(u.y) * rr * w0.w),
+                          pack_bf16x2(bf16lo(u.z) * rr * w1.x, bf16hi(u.z) * rr * w1.y), pack_bf16x2(bf16lo(u.w) * rr * w1.z, bf16hi(u.w) * rr * w1.w));
+    };
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x * 8; c < QW; c += blockDim.x * 8) sq += sq8(*reinterpret_cast<const uint4*>(qr + c));
+    if (k) for (int c = threadIdx.x * 8; c < KW; c += blockDim.x * 8) sk += sq8(*reinterpret_cast<const uint4*>(k + t * ldkv + c));
+    const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)QW + eps) * win_q_temp(a, r.positions[t]);
+    const float rk = k ? 1.0f / sqrtf(block_sum(sk, red) / (float)KW + eps) : 0.f;
+    for (int c = threadIdx.x * 8; c < QW; c += blockDim.x * 8) *reinterpret_cast<uint4*>(qr + c) = scale8(*reinterpret_cast<const uint4*>(qr + c), rq, qw + c);
+    if (k) for (int c = threadIdx.x * 8; c < KW; c += blockDim.x * 8) *reinterpret_cast<uint4*>(crow + c) = scale8(*reinterpret_cast<const uint4*>(k + t * ldkv + c), rk, kw + c);
+    if (v) for (int c = threadIdx.x * 8; c < VW; c += blockDim.x * 8) *reinterpret_cast<uint4*>(crow + KW + c) = *reinterpret_cast<const uint4*>(v + t * ldkv + c);
+}
+
 // score modifiers shared by every form: s is the scaled score of the query at position p (head h) with the key at position j
 __device__ __forceinline__ float win_head_slope(const HyWinAttn& a, int h) { return a.slope_exp > 0.f ? exp2f(-a.slope_exp * (float)(h + 1) / (float)a.heads) : 0.f; }
 __device__ __forceinline__ float win_tanh(float x) {          // 1 - 2 / (e^2x + 1): relative error of a few fp32 ulps from the SFU exponent and a full division
@@ -650,6 +683,10 @@ cudaError_t hy_win_prep(bool f32, const HyWinAttn& a, void* q, int ldq, const vo
                         const HyRows& r, cudaStream_t s) {
     if (r.T <= 0 || (!a.qk_norm && !k && a.q_temp_every <= 0)) return cudaSuccess;
     using bf = __nv_bfloat16;
+    if (a.qk_norm == 2 && !f32 && (a.heads * a.maps * a.dim) % 8 == 0 && (a.kv_heads * a.maps * a.dim) % 8 == 0 && (a.kv_heads * a.vdim) % 8 == 0 && ldq % 8 == 0 && ldkv % 8 == 0 &&
+        ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(q_norm_w) |
+          reinterpret_cast<uintptr_t>(k_norm_w)) & 15) == 0)
+        return launch_plain(hy_win_prep_whole_vec8_kernel, dim3(r.T), dim3(128), 0, s, a, (bf*)q, ldq, (const bf*)k, (const bf*)v, ldkv, q_norm_w, k_norm_w, eps, (bf*)cache, r);
     if (a.qk_norm == 2)
         return f32 ? launch_plain(hy_win_prep_whole_kernel<float>, dim3(r.T), dim3(128), 0, s, a, (float*)q, ldq, (const float*)k, (const float*)v, ldkv, q_norm_w, k_norm_w, eps, (float*)cache, r)
                    : launch_plain(hy_win_prep_whole_kernel<bf>, dim3(r.T), dim3(128), 0, s, a, (bf*)q, ldq, (const bf*)k, (const bf*)v, ldkv, q_norm_w, k_norm_w, eps, (bf*)cache, r);
