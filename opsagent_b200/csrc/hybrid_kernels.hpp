@@ -1,8 +1,10 @@
-// hybrid_kernels.hpp — launch API of the kernels behind the hybrid decoder family (hybrid_kernels.cu, hybrid_window.cu): layer norm and RMS
+// hybrid_kernels.hpp — launch API of the kernels behind the hybrid decoder family (hybrid_kernels.cu, hybrid_window.cu, hybrid_linear.cu): layer norm and RMS
 // norm, latent attention over a paged latent cache, windowed attention over paged keys and values (sliding window, kept first tokens,
-// differential maps, sink, output gates), causal short convolutions with carried tails, the linear recurrences (gated delta rule with
-// per-channel decay, Mamba-2), gated group norms, the routers (group-limited sigmoid; softmax over the chosen logits) and the routed experts
-// (SwiGLU; squared ReLU).  Each mechanism takes its sizes and constants as arguments.
+// differential maps, sink, output gates, soft cap and distance slope on the scores, a norm over the whole projection, a query temperature),
+// causal short convolutions with carried tails, the linear recurrences (gated delta rule with per-channel decay, Mamba-2, gated linear
+// attention, retention, the xLSTM matrix memory with its normaliser and running maximum) and their operand kernels (hybrid_linear.cu), gated
+// group norms, the norm after the sum of post-norm designs, the routers (group-limited sigmoid; softmax over the chosen logits; a table of
+// token ids) and the routed experts (SwiGLU; squared ReLU).  Each mechanism takes its sizes and constants as arguments.
 //
 // `f32` selects the activation / matrix element type: false = bf16 storage with fp32 accumulation, true = everything in fp32.  What must be
 // fp32 in both modes (residual stream, norms, softmax, router, recurrent state, decays, gates of a recurrence) always is.
@@ -59,7 +61,8 @@ cudaError_t hy_post_norm(bool f32, float* x, float beta, const float* y1, const 
 struct HyWinAttn { int heads, kv_heads, dim, vdim, maps, window, keep_first, qk_norm, gate; float scale, lambda, out_scale; float softcap = 0.f, slope_exp = 0.f, q_temp_coef = 0.f; int q_temp_every = 0; };
 bool hy_win_supported(const HyWinAttn& a);
 // q [T, ldq] (head by head, map by map): RMS-normed in place with q_norm_w when qk_norm; k / v [T, ldkv] (null: this layer reads a cache
-// another layer fills): keys normed alike with k_norm_w, both stored at cache row slots[t]
+// another layer fills): keys normed alike with k_norm_w, both stored at cache row slots[t].  qk_norm = 2: one norm over the row's whole q (k) projection,
+// weights of that size, then the query temperature
 cudaError_t hy_win_prep(bool f32, const HyWinAttn& a, void* q, int ldq, const void* k, const void* v, int ldkv, const float* q_norm_w, const float* k_norm_w, float eps, void* cache,
                         const HyRows& r, cudaStream_t s);
 // plain form (any sizes, both element types; prefill rows and decoding rows alike): out[t, head * vdim ..] in the activation type
