@@ -27,6 +27,8 @@ OA_DEVINL float bf16_bits_to_f32(uint16_t h) { return __uint_as_float(((uint32_t
 OA_DEVINL float bf16lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 OA_DEVINL float bf16hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 // pack two fp32 -> bf16x2 (lo = a, hi = b), RNE (cvt.rn.bf16x2.f32 takes hi operand first)
+// the tanh form of GELU: 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+OA_DEVINL float gelu_tanh_f32(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
 OA_DEVINL uint32_t pack_bf16x2(float a, float b) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));

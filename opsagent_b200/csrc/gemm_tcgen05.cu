@@ -164,6 +164,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tcgen05_kernel(const __grid
                             if (p.store_act == 1) {
 #pragma unroll
                                 for (int i = 0; i < 8; ++i) { const float r = fmaxf(f[i], 0.f); f[i] = r * r; }
+                            } else if (p.store_act == 2) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) f[i] = gelu_tanh_f32(f[i]);
                             }
                             uint4 o;
                             o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
@@ -496,6 +499,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_persistent_kernel(const 
                                 if (p.store_act == 1) {
 #pragma unroll
                                     for (int k = 0; k < 8; ++k) { const float r = fmaxf(f[k], 0.f); f[k] = r * r; }
+                                } else if (p.store_act == 2) {
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k) f[k] = gelu_tanh_f32(f[k]);
                                 }
                             } else {
                                 const uint4 rr = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.resid) + (size_t)row * p.ldr + col);

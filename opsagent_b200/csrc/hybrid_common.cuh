@@ -19,6 +19,7 @@ __device__ __forceinline__ void stf(float* p, float v) { *p = v; }
 __device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float siluf_(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float gelu_tanhf_(float z) { return gelu_tanh_f32(z); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 // sum over the block (blockDim.x <= 1024, a multiple of 32); every thread gets the result
 __device__ __forceinline__ float block_sum(float v, float* red) {

@@ -7,7 +7,12 @@
 // logits) and "Rofizen" (norm after the sum: x <- norm(alpha x + sublayer(x)), mixer and feed-forward in sequence; mixers: gated linear
 // attention with a decay per key channel, retention with a fixed decay per head and rotate-half rotary, or causal soft-capped attention with
 // a distance penalty beside an xLSTM matrix memory; feed-forward: dense squared-ReLU, or SwiGLU experts chosen by a table of token ids plus
-// a gated shared expert).  Every size and constant is read from the checkpoint folder's config.json; nothing here is specific to one checkpoint.
+// a gated shared expert).  "Gosavik": pre-norm sublayers in sequence (x += mixer(rms1(x)), x += ff(rms2(x))) over several residual streams
+// joined by learned coefficients (hyper-connections), a token shift in front of every mixer, a looped block without re-injection; mixers:
+// latent attention with a low-rank query, rotate-half rotary with YaRN-scaled frequencies, a sliding window, a sink and a per-channel output
+// gate, or causal grouped-query attention with projection biases, short convolutions on q / k / v, interleaved rotary, rotated values
+// and a sink; feed-forward: dense with the tanh form of GELU.
+// Every size and constant is read from the checkpoint folder's config.json; nothing here is specific to one checkpoint.
 #pragma once
 #include <cstdio>
 #include <fstream>
@@ -37,7 +42,11 @@ struct HyLinear {
     int norm = HY_LIN_NORM_HEAD_WEIGHT, gate_silu = 1;      // output gate: silu (1) or sigmoid (0) of a projection, per channel
     bool q_scaled = true, k_scaled = false;                  // dim^-1/2 on q, or on k (after the rotation)
 };
-enum HyExpertAct : int { HY_EXPERT_SWIGLU = 0, HY_EXPERT_RELU2 = 1 };                       // down(silu(gate x) * up x) / down(relu(up x)^2)
+enum HyExpertAct : int { HY_EXPERT_SWIGLU = 0, HY_EXPERT_RELU2 = 1, HY_EXPERT_GELU_TANH = 2 };     // down(silu(gate x) * up x) / down(relu(up x)^2) / down(gelu_tanh(up x))
+enum HyRotLayout : int { HY_ROT_INTERLEAVED = 0, HY_ROT_HALVES = 1 };                         // channel 2i pairs with 2i + 1 / channel i with i + dims / 2
+// YaRN: with where(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1) and
+// ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), frequency i is f_i / factor * ramp_i + f_i (1 - ramp_i); cos and sin carry the amplitude 0.1 ln(factor) + 1
+struct HyRotScaling { bool on = false; float factor = 1.f, original = 0.f, fast = 0.f, slow = 0.f; };
 enum HyGate : int { HY_GATE_NONE = 0, HY_GATE_CHANNEL = 1, HY_GATE_HEAD = 2 };
 
 struct HyMoe {
@@ -65,11 +74,18 @@ struct HyLayer {
     // q_temp_every > 0: q at position p is multiplied by 1 + q_temp_coef ln(floor((p + 1) / q_temp_every) + 1).  out_bias: bias of the output projection
     int maps = 1, window = 0, keep_first = 0, qk_norm = 0, bias = 0, sink = 0, gate = HY_GATE_NONE, kv_from = -1;
     float diff = 0.f, softcap = 0.f, slope_exp = 0.f, q_temp_coef = 0.f; int q_temp_every = 0, out_bias = 0;
+    // latent attention, optional parts: q_rank > 0: queries through a latent, q = W_uq rms_norm(W_dq h); rot_layout / rot_scaling: pairing and
+    // YaRN scaling of the rotary; window > 0: position i sees j with 0 <= i - j < window; sink; gate = HY_GATE_CHANNEL: sigmoid(W_g h) per channel.
+    // windowed attention, optional parts: conv > 0: a short causal convolution (no bias, no activation) on every channel of q, k and v, right
+    // after the projection; rot_dims > 0: rotary on the first rot_dims channels of every query / key head; v_rot: the value of position j is
+    // cached turned by j over all vdim channels (pair m by j rot_base^(-2m / vdim)), a head's output at position i is turned back by -i
+    int q_rank = 0, rot_layout = HY_ROT_INTERLEAVED, v_rot = 0;
+    HyRotScaling rot_scaling;
     HyLinear lin;                         // HY_LINEAR_ATTENTION, and the memory side of HY_ATTENTION_BESIDE_MEMORY (whose attention side uses the fields above)
     HyMoe moe;
 };
 
-struct HyRun { int layer = 0, pass = -1; bool first_of_pass = false; int cache_idx = -1, state_idx = -1; bool cache_owner = false; };   // one execution of a layer (a looped layer runs once per pass)
+struct HyRun { int layer = 0, pass = -1; bool first_of_pass = false; int cache_idx = -1, state_idx = -1; bool cache_owner = false; int index = 0; };   // one execution of a layer (a looped layer runs once per pass)
 
 struct HybridConfig {
     std::string dir;                      // checkpoint folder (config.json [+ model.safetensors]; without the latter the weights are seeded)
@@ -80,6 +96,13 @@ struct HybridConfig {
     bool two_norms = false;               // mixer and feed-forward each read their own norm of the same residual
     float embed_scale = 1.f, logit_softcap = 0.f;      // x = embed[token] * scale; logits <- cap * tanh(logits / cap) (0: none)
     bool post_norm = false; float post_alpha = 1.f;    // norm after the sum: x <- norm1(alpha x + mixer(x)), x <- norm2(alpha x + ff(x)); the sublayers read x itself
+    // sublayers in sequence, each on its own norm of the residual it finds: x <- x + mixer(norm1(x)), then x <- x + ff(norm2(x)).
+    // streams > 0 (hyper-connections): the residual is `streams` copies x_1..x_s of the embedding; sublayer q reads u = sum_s in_q[s] x_s and
+    // every stream becomes x_t <- sum_s mix_q[s, t] x_s + out_q[t] sublayer(norm(u)); after the last layer x = sum_s x_s.
+    // token_shift: the mixer's input h_t (after the norm) is replaced by h_t + (h_(t-1) - h_t) * shift, h_(t-1) as it was before its own
+    // replacement (zeros before the first token); every layer execution carries the last h of a sequence in its state slot.
+    bool sequential = false, token_shift = false; int streams = 0;
+    bool loop_reinject = true;                          // a looped block re-injects the embedding before every pass (x <- W_in [x ; x0] + step[pass])
     std::vector<HyLayer> layers;
     int loop_start = 0, loop_stop = 0, loop_times = 0;    // times == 0: no looped block
     std::vector<HyRun> runs;
@@ -114,6 +137,7 @@ struct HybridConfig {
         if (architecture == "Ratasun") return "ratasun";
         if (architecture == "Zurevik") return "zurevik";
         if (architecture == "Rofizen") return "rofizen";
+        if (architecture == "Gosavik") return "gosavik";
         return "";
     }
 
@@ -123,7 +147,11 @@ struct HybridConfig {
         HybridConfig c; c.dir = dir;
         c.arch = registry_key(j.str("architecture"));
         if (c.arch.empty()) throw std::runtime_error("config.json: unknown architecture '" + j.str("architecture") + "'");
-        const bool zu = c.arch == "zurevik", ro = c.arch == "rofizen";
+        const bool zu = c.arch == "zurevik", ro = c.arch == "rofizen", go = c.arch == "gosavik";
+        if (go) {
+            c.norm = HY_RMS_NORM; c.sequential = true; c.token_shift = true; c.loop_reinject = false;
+            if (j.get("streams") && j.get("streams")->t == Json::Num) { c.streams = integer(j, "streams", "the model"); if (c.streams < 1 || c.streams > 8) throw std::runtime_error("config.json: streams must be 1 .. 8"); }
+        }
         if (zu) { c.norm = HY_RMS_NORM; c.two_norms = true; }
         if (ro) { c.post_norm = true; c.post_alpha = (float)num(j, "postln_alpha", "the model"); }
         if (const Json* e = j.get("embedding")) if (e->t == Json::Obj && e->get("scale")) c.embed_scale = (float)num(*e, "scale", "embedding");
@@ -143,6 +171,17 @@ struct HybridConfig {
                 const Json& r = obj(m, "rot", type.c_str());
                 l.rot_base = (float)num(r, "base", "rot"); l.rot_dims = integer(r, "dims", "rot");
                 if (l.rot_dims > l.rot_dim || (l.rot_dims & 1)) throw std::runtime_error("config.json: rot.dims must be even and <= rot_dim");
+                if (go) {
+                    l.q_rank = integer(m, "q_rank", type.c_str()); l.rot_layout = HY_ROT_HALVES; l.sink = 1; l.gate = HY_GATE_CHANNEL;
+                    if (const Json* mk = m.get("mask")) if (mk->t == Json::Obj) { l.window = integer(*mk, "size", "mask"); if (l.window < 1) throw std::runtime_error("config.json: mask.size must be at least 1"); }
+                    if (const Json* sc = r.get("scaling")) if (sc->t == Json::Obj) {
+                        l.rot_scaling.on = true; l.rot_scaling.factor = (float)num(*sc, "factor", "scaling"); l.rot_scaling.original = (float)num(*sc, "original", "scaling");
+                        l.rot_scaling.fast = (float)num(*sc, "fast", "scaling"); l.rot_scaling.slow = (float)num(*sc, "slow", "scaling");
+                        if (!(l.rot_scaling.factor > 0.f) || !(l.rot_scaling.original > 0.f) || !(l.rot_scaling.fast > 0.f) || !(l.rot_scaling.slow > 0.f) || !(l.rot_base > 1.f))
+                            throw std::runtime_error("config.json: bad rotary scaling");
+                    }
+                    if (l.q_rank <= 0 || l.dim < 0 || l.rot_dim < 0 || l.dim + l.rot_dim <= 0 || l.kv_rank <= 0 || l.kv_rank > 1024) throw std::runtime_error("config.json: bad latent attention sizes");
+                }
             } else if (type == "channel_delta") {
                 l.type = HY_CHANNEL_DELTA;
                 l.heads = integer(m, "heads", type.c_str()); l.kv_heads = integer(m, "kv_heads", type.c_str()); l.dim = integer(m, "dim", type.c_str());
@@ -153,6 +192,17 @@ struct HybridConfig {
                 l.heads = integer(m, "heads", type.c_str()); l.vdim = integer(m, "vdim", type.c_str()); l.state = integer(m, "state", type.c_str());
                 l.groups = integer(m, "groups", type.c_str()); l.norm_groups = integer(m, "norm_groups", type.c_str()); l.conv = integer(m, "conv", type.c_str());
                 if (l.groups <= 0 || l.heads % l.groups || l.norm_groups <= 0 || (l.heads * l.vdim) % l.norm_groups) throw std::runtime_error("config.json: groups must divide heads, norm_groups the inner size");
+            } else if (go && type == "attention") {
+                // causal grouped-query attention: projection biases, short convolutions, interleaved rotary on queries and keys, rotated values, a sink per head
+                l.type = HY_WINDOW_ATTENTION;
+                l.heads = integer(m, "heads", type.c_str()); l.kv_heads = integer(m, "kv_heads", type.c_str()); l.dim = integer(m, "dim", type.c_str());
+                l.vdim = integer(m, "vdim", type.c_str()); l.scale = (float)num(m, "scale", type.c_str()); l.conv = integer(m, "conv", type.c_str());
+                const Json& r = obj(m, "rot", type.c_str());
+                l.rot_base = (float)num(r, "base", "rot"); l.rot_dims = integer(r, "dims", "rot"); l.rot_layout = HY_ROT_INTERLEAVED;
+                l.window = 1 << 30; l.bias = 1; l.out_bias = 1; l.sink = 1; l.v_rot = 1;
+                if (const Json* mk = m.get("mask")) if (mk->t == Json::Obj) { l.window = integer(*mk, "size", "mask"); if (l.window < 1) throw std::runtime_error("config.json: mask.size must be at least 1"); }
+                if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.vdim > 256 || (l.vdim & 1) || l.dim > 1024 || l.rot_dims < 0 || l.rot_dims > l.dim || (l.rot_dims & 1) || l.conv < 1 || l.conv > 16 || !(l.rot_base > 0.f))
+                    throw std::runtime_error("config.json: bad attention sizes");
             } else if (type == "attention" || type == "attention_2") {
                 // "attention": differential (two score maps), query/key norm, kept first tokens, gate per channel;
                 // "attention_2": one map, projection biases, a sink per head, gate per head, optionally another layer's keys and values
@@ -205,12 +255,12 @@ struct HybridConfig {
             const bool recurrent = l.type == HY_CHANNEL_DELTA || l.type == HY_MAMBA2;
             if (l.heads <= 0 || l.vdim <= 0 || (recurrent && (l.conv < 1 || l.conv > 16))) throw std::runtime_error("config.json: bad mixer sizes");
             const Json* mj = lj.get("mlp");
-            if (mj && mj->t == Json::Obj && ro && mj->str("kind") == "dense") {
-                l.moe.present = true; l.moe.dense = true; l.moe.act = HY_EXPERT_RELU2; l.moe.experts = 1; l.moe.top = 1;
+            if (mj && mj->t == Json::Obj && (ro || go) && mj->str("kind") == "dense") {
+                l.moe.present = true; l.moe.dense = true; l.moe.act = go ? HY_EXPERT_GELU_TANH : HY_EXPERT_RELU2; l.moe.experts = 1; l.moe.top = 1;
                 l.moe.ff = integer(*mj, "ff", "mlp");
                 if (l.moe.ff <= 0) throw std::runtime_error("config.json: bad feed-forward width");
             } else if (mj && mj->t == Json::Obj) {
-                if (mj->str("kind") != "moe") throw std::runtime_error("config.json: unknown mlp kind '" + mj->str("kind") + "'");
+                if (go || mj->str("kind") != "moe") throw std::runtime_error("config.json: unknown mlp kind '" + mj->str("kind") + "'");
                 const Json& r = obj(*mj, "router", "mlp");
                 l.moe.present = true; l.moe.ff = integer(obj(*mj, "expert", "mlp"), "ff", "expert");
                 l.moe.experts = integer(r, "experts", "router"); l.moe.top = integer(r, "top", "router");
@@ -241,9 +291,13 @@ struct HybridConfig {
                 for (const HyRun& o : c.runs) if (o.layer == l.kv_from) r.cache_idx = o.cache_idx;
                 if (r.cache_idx < 0 || (c.loop_times > 0 && layer >= c.loop_start && layer < c.loop_stop) || (c.loop_times > 0 && l.kv_from >= c.loop_start && l.kv_from < c.loop_stop))
                     throw std::runtime_error("config.json: a layer that reads another layer's cache cannot be part of a looped block");
-            } else if (l.type == HY_LATENT_ATTENTION || l.type == HY_WINDOW_ATTENTION) { r.cache_idx = c.n_caches++; r.cache_owner = true; }
+            } else if (l.type == HY_LATENT_ATTENTION || l.type == HY_WINDOW_ATTENTION) {
+                r.cache_idx = c.n_caches++; r.cache_owner = true;
+                if (l.type == HY_WINDOW_ATTENTION && l.conv > 1) r.state_idx = c.n_states++;        // the convolutions' tails
+            }
             else if (l.type == HY_ATTENTION_BESIDE_MEMORY) { r.cache_idx = c.n_caches++; r.cache_owner = true; r.state_idx = c.n_states++; }     // a cache for the attention side, a state for the memory side
             else r.state_idx = c.n_states++;
+            r.index = (int)c.runs.size();
             c.runs.push_back(r);
         };
         for (int i = 0; i < (int)c.layers.size();) {

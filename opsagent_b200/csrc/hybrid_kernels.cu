@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(256) hy_gemm_kernel(const TA* __restrict__ A, 
             if (n >= N) continue;
             float v = acc[i][j] * alpha + (bias ? bias[n] : 0.f);
             if (act == 1) { v = fmaxf(v, 0.f); v *= v; }
+            else if (act == 2) v = gelu_tanhf_(v);
             const long long at = (long long)blockIdx.z * sC + (long long)m * ldc + n;
             if (MODE == HY_STORE) stf(reinterpret_cast<TA*>(Cv) + at, v);
             else if (MODE == HY_STORE_F32) reinterpret_cast<float*>(Cv)[at] = v;
@@ -137,15 +138,21 @@ __global__ void __launch_bounds__(128) hy_mla_prep_kernel(HyLatentAttn a, const 
     const float* cs = rope_cos + (long long)pos * half; const float* sn = rope_sin + (long long)pos * half;
     for (int i = threadIdx.x; i < rot; i += blockDim.x) {          // shared rotated key
         float v;
-        if (i < 2 * half) { const int p = i >> 1; const float u0 = ldf(c + R + 2 * p), u1 = ldf(c + R + 2 * p + 1); v = (i & 1) ? (u1 * cs[p] + u0 * sn[p]) : (u0 * cs[p] - u1 * sn[p]); }
-        else v = ldf(c + R + i);
+        if (i < 2 * half) {
+            const bool second = a.rot_layout ? i >= half : (i & 1); const int p = a.rot_layout ? (second ? i - half : i) : i >> 1;
+            const float u0 = ldf(c + R + (a.rot_layout ? p : 2 * p)), u1 = ldf(c + R + (a.rot_layout ? p + half : 2 * p + 1));
+            v = second ? (u1 * cs[p] + u0 * sn[p]) : (u0 * cs[p] - u1 * sn[p]);
+        } else v = ldf(c + R + i);
         stf(dst + R + i, v);
     }
     for (int i = threadIdx.x; i < a.heads * rot; i += blockDim.x) {   // rotated query parts
         const int h = i / rot, d = i - h * rot; const TA* qh = q + (long long)t * ldq + (long long)h * (a.dim + rot) + a.dim;
         float v;
-        if (d < 2 * half) { const int p = d >> 1; const float u0 = ldf(qh + 2 * p), u1 = ldf(qh + 2 * p + 1); v = (d & 1) ? (u1 * cs[p] + u0 * sn[p]) : (u0 * cs[p] - u1 * sn[p]); }
-        else v = ldf(qh + d);
+        if (d < 2 * half) {
+            const bool second = a.rot_layout ? d >= half : (d & 1); const int p = a.rot_layout ? (second ? d - half : d) : d >> 1;
+            const float u0 = ldf(qh + (a.rot_layout ? p : 2 * p)), u1 = ldf(qh + (a.rot_layout ? p + half : 2 * p + 1));
+            v = second ? (u1 * cs[p] + u0 * sn[p]) : (u0 * cs[p] - u1 * sn[p]);
+        } else v = ldf(qh + d);
         q_abs[((long long)t * a.heads + h) * E + R + d] = v;
     }
 }
@@ -168,7 +175,8 @@ __global__ void __launch_bounds__(128) hy_mla_attention_kernel(HyLatentAttn a, c
     float m = -INFINITY, l = 0.f, acc[MLA_ACC];
 #pragma unroll
     for (int i = 0; i < MLA_ACC; ++i) acc[i] = 0.f;
-    for (int j = warp; j <= pos; j += 4) {
+    const int j_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;         // a warp's keys depend on the row's position only
+    for (int j = j_lo + warp; j <= pos; j += 4) {
         const TA* kr = cache + ((long long)bt[j >> 6] * 64 + (j & 63)) * E;
         float d = 0.f;
         for (int i = lane; i < E; i += 32) d = fmaf(qs[i], ldf(kr + i), d);
@@ -182,9 +190,11 @@ __global__ void __launch_bounds__(128) hy_mla_attention_kernel(HyLatentAttn a, c
     for (int i = 0; i < MLA_ACC; ++i) { const int c = lane + 32 * i; if (c < R) macc[warp * R + c] = acc[i]; }
     if (lane == 0) { mm[warp] = m; ll[warp] = l; }
     __syncthreads();
-    float M = fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3])), L = 0.f, f[4];
+    const float sk = a.sink ? a.sink[h] : -INFINITY;                        // the sink: one more term of the denominator, no value
+    float M = fmaxf(fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3])), sk), L = 0.f, f[4];
 #pragma unroll
     for (int w = 0; w < 4; ++w) { f[w] = mm[w] == -INFINITY ? 0.f : expf(mm[w] - M); L += f[w] * ll[w]; }
+    if (a.sink) L += expf(sk - M);
     const float inv = 1.0f / L;
     for (int c = threadIdx.x; c < R; c += blockDim.x) {
         float v = 0.f;
@@ -227,7 +237,9 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
     const int k0 = sp.tile_k0 ? sp.tile_k0[blockIdx.x] : 0, k1 = sp.tile_k0 ? sp.tile_k1[blockIdx.x] : 0, slot = sp.tile_k0 ? sp.tile_slot[blockIdx.x] : -1;
     int max_pos = r.positions[row0 + (q0 + nq - 1) / H];
     if (k1 > 0 && k1 - 1 < max_pos) max_pos = k1 - 1;
-    const int kt0 = k0 / MLA_KT, n_kt = max_pos / MLA_KT + 1;
+    const int win = a.window > 0 ? a.window : 0x40000000;
+    const int first_vis = max(k0, r.positions[row0 + q0 / H] - win + 1);       // the first cache row any query of the tile sees
+    const int kt0 = max(first_vis, 0) / MLA_KT, n_kt = max_pos / MLA_KT + 1;
     const int32_t* bt = r.block_tables + (long long)seq * r.max_pages_per_seq;
     auto load_tile = [&](int kt, int buf) {
         const int chunks = E / 8;
@@ -273,15 +285,16 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
             for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const int key = kt * MLA_KT + nb * 8 + (lane & 3) * 2 + (c & 1);
-                    if (key > (c < 2 ? p_lo : p_hi)) s[nb][c] = -INFINITY;
+                    const int key = kt * MLA_KT + nb * 8 + (lane & 3) * 2 + (c & 1), pq = c < 2 ? p_lo : p_hi;
+                    if (key > pq || pq - key >= win) s[nb][c] = -INFINITY;
                     if (c < 2) mx_lo = fmaxf(mx_lo, s[nb][c]); else mx_hi = fmaxf(mx_hi, s[nb][c]);
                 }
             mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-            const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);       // finite: the first row of a CTA's range is visible to each of its queries
+            const float t_lo = fmaxf(m_lo, mx_lo), t_hi = fmaxf(m_hi, mx_hi);
+            const float n_lo = t_lo == -INFINITY ? 0.f : t_lo, n_hi = t_hi == -INFINITY ? 0.f : t_hi;       // a query whose window starts behind this tile has seen nothing yet
             const float c_lo = exp2f(m_lo - n_lo), c_hi = exp2f(m_hi - n_hi);
-            m_lo = n_lo; m_hi = n_hi;
+            m_lo = t_lo; m_hi = t_hi;
             float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
@@ -322,12 +335,17 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
         }
         return;
     }
-    const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int qi = half ? q_hi : q_lo;
         if (qi >= nq) continue;
-        const int row = row0 + (q0 + qi) / H, h = (q0 + qi) % H; const float inv = half ? i_hi : i_lo;
+        const int row = row0 + (q0 + qi) / H, h = (q0 + qi) % H;
+        float l = half ? l_hi : l_lo, up = 1.f;
+        if (a.sink) {                 // the sink joins the denominator (scores are kept in base-2 units)
+            const float m = half ? m_hi : m_lo, s2 = a.sink[h] * 1.4426950408889634f, M = fmaxf(m, s2);
+            up = m == -INFINITY ? 0.f : exp2f(m - M); l = l * up + exp2f(s2 - M);
+        }
+        const float inv = l > 0.f ? up / l : 0.f;
         __nv_bfloat16* dst = lat_out + ((long long)row * H + h) * R + vbase + (lane & 3) * 2;
 #pragma unroll
         for (int nb = 0; nb < NVB; ++nb) *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16x2(o[nb][half * 2] * inv, o[nb][half * 2 + 1] * inv);
@@ -336,12 +354,13 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
 
 // joins the parts of a decoding row: out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p, parts in order
 __global__ void __launch_bounds__(128) hy_mla_merge_kernel(const int32_t* item_row, const int32_t* item_slot0, const int32_t* item_parts, const float* ws_o,
-                                                           const float* ws_ml, __nv_bfloat16* lat_out, int H, int R) {
+                                                           const float* ws_ml, __nv_bfloat16* lat_out, int H, int R, const float* sink) {
     HY_PDL();
     const int row = item_row[blockIdx.x], slot0 = item_slot0[blockIdx.x], P = item_parts[blockIdx.x], h = blockIdx.y;
-    float M = -INFINITY;
+    const float s2 = sink ? sink[h] * 1.4426950408889634f : -INFINITY;       // the sink, in the partials' base-2 units
+    float M = s2;
     for (int p = 0; p < P; ++p) M = fmaxf(M, ws_ml[((long long)(slot0 + p) * H + h) * 2]);
-    float L = 0.f;
+    float L = sink ? exp2f(s2 - M) : 0.f;
     for (int p = 0; p < P; ++p) { const float* ml = ws_ml + ((long long)(slot0 + p) * H + h) * 2; L += exp2f(ml[0] - M) * ml[1]; }
     const float inv = 1.0f / L;
     for (int c = threadIdx.x; c < R; c += blockDim.x) {
@@ -388,7 +407,8 @@ __global__ void __launch_bounds__(128) hy_mha_prefill_mma_kernel(HyLatentAttn a,
     }
     for (int qi = tid; qi < MLA_MQ; qi += 128) qpos[qi] = qi < nq ? r.positions[row0 + qi] : 0;
     const int max_pos = r.positions[row0 + nq - 1];
-    const int n_kt = max_pos / KT + 1;
+    const int win = a.window > 0 ? a.window : 0x40000000;
+    const int kt_first = max(0, r.positions[row0] - win + 1) / KT, n_kt = max_pos / KT + 1;      // tiles before the first query's window hold nothing visible
     auto load_tile = [&](int kt, int buf) {
         const int kc = DQ / 8, nc = DN / 8, vc = VD / 8;
         for (int idx = tid; idx < KT * (kc + vc); idx += 128) {
@@ -408,8 +428,8 @@ __global__ void __launch_bounds__(128) hy_mha_prefill_mma_kernel(HyLatentAttn a,
     for (int i = 0; i < NVB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
     const bool active = 16 * warp < nq;
-    load_tile(0, 0);
-    for (int kt = 0; kt < n_kt; ++kt) {
+    load_tile(kt_first, kt_first & 1);
+    for (int kt = kt_first; kt < n_kt; ++kt) {
         if (kt + 1 < n_kt) { load_tile(kt + 1, (kt + 1) & 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
         else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
@@ -434,15 +454,16 @@ __global__ void __launch_bounds__(128) hy_mha_prefill_mma_kernel(HyLatentAttn a,
             for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const int key = kt * KT + nb * 8 + (lane & 3) * 2 + (c & 1);
-                    s[nb][c] = key > (c < 2 ? p_lo : p_hi) ? -INFINITY : s[nb][c] * qscale;
+                    const int key = kt * KT + nb * 8 + (lane & 3) * 2 + (c & 1), pq = c < 2 ? p_lo : p_hi;
+                    s[nb][c] = (key > pq || pq - key >= win) ? -INFINITY : s[nb][c] * qscale;
                     if (c < 2) mx_lo = fmaxf(mx_lo, s[nb][c]); else mx_hi = fmaxf(mx_hi, s[nb][c]);
                 }
             mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-            const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);       // finite: key 0 is visible to every query and lies in tile 0
+            const float t_lo = fmaxf(m_lo, mx_lo), t_hi = fmaxf(m_hi, mx_hi);
+            const float n_lo = t_lo == -INFINITY ? 0.f : t_lo, n_hi = t_hi == -INFINITY ? 0.f : t_hi;       // a query whose window starts behind this tile has seen nothing yet
             const float c_lo = exp2f(m_lo - n_lo), c_hi = exp2f(m_hi - n_hi);
-            m_lo = n_lo; m_hi = n_hi;
+            m_lo = t_lo; m_hi = t_hi;
             float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
             for (int nb = 0; nb < 4; ++nb) {
@@ -470,12 +491,16 @@ __global__ void __launch_bounds__(128) hy_mha_prefill_mma_kernel(HyLatentAttn a,
     if (!active) return;
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int qi = 16 * warp + (lane >> 2) + half * 8;
         if (qi >= nq) continue;
-        const float inv = half ? i_hi : i_lo;
+        float l = half ? l_hi : l_lo, up = 1.f;
+        if (a.sink) {                 // the sink joins the denominator (scores are kept in base-2 units)
+            const float m = half ? m_hi : m_lo, s2 = a.sink[h] * 1.4426950408889634f, M = fmaxf(m, s2);
+            up = m == -INFINITY ? 0.f : exp2f(m - M); l = l * up + exp2f(s2 - M);
+        }
+        const float inv = l > 0.f ? up / l : 0.f;
         __nv_bfloat16* dst = mix + (long long)(row0 + qi) * ld_mix + h * VD + (lane & 3) * 2;
 #pragma unroll
         for (int nb = 0; nb < NVB; ++nb) *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16x2(o[nb][half * 2] * inv, o[nb][half * 2 + 1] * inv);
@@ -506,7 +531,7 @@ __device__ __forceinline__ float conv_input(const TA* in, int ld_in, int C, cons
     return ldf(tail + (long long)(taps - 1 + src) * C + c);
 }
 template <typename TA>
-__global__ void hy_conv_silu_kernel(const TA* in, int ld_in, int C, const float* w, const float* bias, int taps, TA* out, int ld_out, const TA* tails, HyRows r) {
+__global__ void hy_conv_silu_kernel(const TA* in, int ld_in, int C, const float* w, const float* bias, int taps, TA* out, int ld_out, const TA* tails, HyRows r, int act) {
     HY_PDL();
     const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (c >= C) return;
@@ -514,7 +539,7 @@ __global__ void hy_conv_silu_kernel(const TA* in, int ld_in, int C, const float*
     const TA* tail = tails + (long long)r.seq_state[seq] * (taps - 1) * C;
     float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) acc = fmaf(w[c * taps + j], conv_input(in, ld_in, C, tail, taps, row0, pos0, i - (taps - 1) + j, c), acc);
-    stf(out + (long long)t * ld_out + c, siluf_(acc));
+    stf(out + (long long)t * ld_out + c, act ? siluf_(acc) : acc);
 }
 // bf16 rows of prefill-sized steps whose channels come in aligned groups of 8: a thread computes 8 channels of CONV_ROWS consecutive rows
 // from 16-byte loads, with its taps' weights and the last inputs in registers, so that every input row is read once.  The sum runs over
@@ -527,7 +552,7 @@ __device__ __forceinline__ void bf8_to_f32(const uint4& u, float* f) {
 }
 template <int TAPS>
 __global__ void __launch_bounds__(128) hy_conv_silu_vec8_kernel(const __nv_bfloat16* __restrict__ in, int ld_in, int C, const float* __restrict__ w, const float* __restrict__ bias,
-                                                                 __nv_bfloat16* __restrict__ out, int ld_out, const __nv_bfloat16* __restrict__ tails, HyRows r) {
+                                                                 __nv_bfloat16* __restrict__ out, int ld_out, const __nv_bfloat16* __restrict__ tails, HyRows r, int act) {
     HY_PDL();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8, t0 = blockIdx.y * CONV_ROWS;
     if (c >= C) return;
@@ -559,7 +584,7 @@ __global__ void __launch_bounds__(128) hy_conv_silu_vec8_kernel(const __nv_bfloa
             float a0 = b8[2 * e], a1 = b8[2 * e + 1];
 #pragma unroll
             for (int j = 0; j < TAPS; ++j) { a0 = fmaf(wr[j][2 * e], win[j][2 * e], a0); a1 = fmaf(wr[j][2 * e + 1], win[j][2 * e + 1], a1); }
-            const __nv_bfloat162 h = __floats2bfloat162_rn(siluf_(a0), siluf_(a1));
+            const __nv_bfloat162 h = act ? __floats2bfloat162_rn(siluf_(a0), siluf_(a1)) : __floats2bfloat162_rn(a0, a1);
             o[e] = *reinterpret_cast<const uint32_t*>(&h);
         }
         *reinterpret_cast<uint4*>(out + (long long)t * ld_out + c) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -1180,9 +1205,9 @@ static cudaError_t mla_mma_launch(const HyLatentAttn& a, const float* q_abs, con
                         tile_seq, tile_q0, sp);
 }
 cudaError_t hy_mla_merge(const int32_t* item_row, const int32_t* item_slot0, const int32_t* item_parts, int n_items, const float* ws_o, const float* ws_ml, void* lat_out,
-                         int heads, int kv_rank, cudaStream_t s) {
+                         int heads, int kv_rank, cudaStream_t s, const float* sink) {
     if (n_items <= 0) return cudaSuccess;
-    return launch_plain(hy_mla_merge_kernel, dim3(n_items, heads), dim3(128), 0, s, item_row, item_slot0, item_parts, ws_o, ws_ml, (bf*)lat_out, heads, kv_rank);
+    return launch_plain(hy_mla_merge_kernel, dim3(n_items, heads), dim3(128), 0, s, item_row, item_slot0, item_parts, ws_o, ws_ml, (bf*)lat_out, heads, kv_rank, sink);
 }
 cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, const int32_t* tile_seq,
                                  const int32_t* tile_q0, int n_tiles, const HyMlaSplit& sp, cudaStream_t s) {
@@ -1228,19 +1253,19 @@ cudaError_t hy_mha_prefill(const HyLatentAttn& a, const void* q, int ldq, const 
     return cudaErrorInvalidValue;
 }
 cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out, const void* tails, const HyRows& r,
-                         cudaStream_t s) {
+                         cudaStream_t s, int act) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (!f32 && r.T >= 512 && taps >= 2 && taps <= 4 && C % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && al16(in) && al16(out) && al16(tails)) {
         const dim3 g((C / 8 + 127) / 128, (r.T + CONV_ROWS - 1) / CONV_ROWS);
         switch (taps) {
-            case 2: return launch_plain(hy_conv_silu_vec8_kernel<2>, g, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, (bf*)out, ld_out, (const bf*)tails, r);
-            case 3: return launch_plain(hy_conv_silu_vec8_kernel<3>, g, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, (bf*)out, ld_out, (const bf*)tails, r);
-            default: return launch_plain(hy_conv_silu_vec8_kernel<4>, g, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, (bf*)out, ld_out, (const bf*)tails, r);
+            case 2: return launch_plain(hy_conv_silu_vec8_kernel<2>, g, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, (bf*)out, ld_out, (const bf*)tails, r, act);
+            case 3: return launch_plain(hy_conv_silu_vec8_kernel<3>, g, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, (bf*)out, ld_out, (const bf*)tails, r, act);
+            default: return launch_plain(hy_conv_silu_vec8_kernel<4>, g, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, (bf*)out, ld_out, (const bf*)tails, r, act);
         }
     }
     dim3 grid((C + 127) / 128, r.T);
-    return f32 ? launch_plain(hy_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)in, ld_in, C, w, bias, taps, (float*)out, ld_out, (const float*)tails, r)
-               : launch_plain(hy_conv_silu_kernel<bf>, grid, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, taps, (bf*)out, ld_out, (const bf*)tails, r);
+    return f32 ? launch_plain(hy_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)in, ld_in, C, w, bias, taps, (float*)out, ld_out, (const float*)tails, r, act)
+               : launch_plain(hy_conv_silu_kernel<bf>, grid, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, taps, (bf*)out, ld_out, (const bf*)tails, r, act);
 }
 cudaError_t hy_conv_tails(bool f32, const void* in, int ld_in, int C, int taps, void* tails, const HyRows& r, cudaStream_t s) {
     if (taps <= 1) return cudaSuccess;

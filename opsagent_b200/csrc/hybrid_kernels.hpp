@@ -29,7 +29,7 @@ struct HyRows {
 enum HyGemmMode : int { HY_STORE = 0, HY_STORE_F32 = 1, HY_ACC_F32 = 2 };
 // C[z][M,N] (op)= alpha * A[z][M,K] . B[z][N,K]^T (+ bias[N]), z < batch with element strides sA/sB/sC.  Plain tiled FMA GEMM in fp32
 // accumulation for any sizes: the fp32 mode's matrix product, and the bf16 mode's fallback where a shape does not fit the tensor-core tiles.
-// act = 1: the stored value is relu(.)^2 (HY_STORE / HY_STORE_F32)
+// act = 1: the stored value is relu(.)^2, act = 2: the tanh form of GELU (HY_STORE / HY_STORE_F32)
 cudaError_t hy_gemm(bool f32, int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias,
                     float alpha, int batch, long long sA, long long sB, long long sC, cudaStream_t s, int act = 0);
 
@@ -58,7 +58,15 @@ cudaError_t hy_post_norm(bool f32, float* x, float beta, const float* y1, const 
 // Score modifiers (all optional): softcap > 0: s <- softcap tanh(s / softcap) after the scale; slope_exp > 0: head h then loses
 // 2^(-slope_exp (h + 1) / heads) * (i - j).  qk_norm = 2: one RMS norm over the whole q (k) projection of a row, weights [heads maps dim]
 // ([kv_heads maps dim]); q_temp_every > 0: the query at position p is multiplied by 1 + q_temp_coef ln(floor((p + 1) / q_temp_every) + 1).
-struct HyWinAttn { int heads, kv_heads, dim, vdim, maps, window, keep_first, qk_norm, gate; float scale, lambda, out_scale; float softcap = 0.f, slope_exp = 0.f, q_temp_coef = 0.f; int q_temp_every = 0; };
+// out_rot (1: pairs 2m / 2m + 1, 2: pairs m / m + vdim / 2): every head's output at position i is turned by -i over all vdim channels with the
+// angles of out_cos / out_sin ([position, vdim / 2]) before the gate: the counterpart of values that were cached turned by their own position.
+struct HyWinAttn { int heads, kv_heads, dim, vdim, maps, window, keep_first, qk_norm, gate; float scale, lambda, out_scale; float softcap = 0.f, slope_exp = 0.f, q_temp_coef = 0.f; int q_temp_every = 0;
+                   int out_rot = 0; const float* out_cos = nullptr; const float* out_sin = nullptr; };
+// Rotary preparation of a cached-key/value attention layer (maps = 1, no query / key norm): the first rot_dims channels of every query head (in
+// place) and key head turn by the row's position (layout 0: pairs 2i / 2i + 1, 1: pairs i / i + rot_dims / 2; tables [position, rot_dims / 2]);
+// with v_cos / v_sin ([position, vdim / 2]) every value head turns over all of its channels in the same layout; keys and values go to cache row slots[t].
+struct HyRotary { int dims, layout; const float* cos; const float* sin; const float* v_cos; const float* v_sin; };
+cudaError_t hy_win_rope_prep(bool f32, const HyWinAttn& a, const HyRotary& rot, void* q, int ldq, const void* k, const void* v, int ldkv, void* cache, const HyRows& r, cudaStream_t s);
 bool hy_win_supported(const HyWinAttn& a);
 // q [T, ldq] (head by head, map by map): RMS-normed in place with q_norm_w when qk_norm; k / v [T, ldkv] (null: this layer reads a cache
 // another layer fills): keys normed alike with k_norm_w, both stored at cache row slots[t].  qk_norm = 2: one norm over the row's whole q (k) projection,
@@ -85,6 +93,9 @@ cudaError_t hy_win_decode_mma(const HyWinAttn& a, const void* q, int ldq, const 
 
 struct HyLatentAttn {             // sizes of one latent-attention layer
     int heads, dim, rot_dim, vdim, kv_rank, rot_dims; float scale;
+    // optional parts: window > 0: position i sees j with 0 <= i - j < window (0: every j <= i); rot_layout 1: rotary pairs channel i with
+    // i + rot_dims / 2 instead of 2i with 2i + 1; sink (device, one fp32 logit per head): joins the softmax denominator only, unscaled
+    int window = 0, rot_layout = 0; const float* sink = nullptr;
 };
 // From the q projection (q: [T, ldq], head by head [dim | rot_dim]) and the down projection (ckv: [T, ldc] = [kv_rank | rot_dim]):
 // latent = rmsnorm(ckv[:rank]) * norm_w and the rotated shared key go to cache row slots[t] ([rank + rot_dim] per row); the rotated query
@@ -106,7 +117,7 @@ bool hy_mla_mma_supported(const HyLatentAttn& a);
 cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, const int32_t* tile_seq,
                                  const int32_t* tile_q0, int n_tiles, const HyMlaSplit& sp, cudaStream_t s);
 cudaError_t hy_mla_merge(const int32_t* item_row, const int32_t* item_slot0, const int32_t* item_parts, int n_items, const float* ws_o, const float* ws_ml, void* lat_out,
-                         int heads, int kv_rank, cudaStream_t s);
+                         int heads, int kv_rank, cudaStream_t s, const float* sink = nullptr);
 
 // Prefill form (bf16; dim and rot_dim multiples of 8, their sum of 16, vdim 16 / 32 / 64 / 128): hy_gather_ctx copies the cache rows 0..ctx-1 of
 // the sequences with seq_base[s] >= 0 to lat_ctx[seq_base[s] + j]; a GEMM makes kv_ctx = lat_ctx[:, :rank] . [W_uk ; W_uv]^T ([rows, heads dim |
@@ -120,8 +131,9 @@ cudaError_t hy_mha_prefill(const HyLatentAttn& a, const void* q, int ldq, const 
 
 // y = silu(causal conv over time of `in` per channel (+ bias)); inputs before a sequence's first row of this step come from its tail
 // (the last taps-1 inputs of earlier steps; zeros at the start of a sequence).  hy_conv_tails then stores the new tails.
+// act = 0: no activation (y is the convolution itself)
 cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out,
-                         const void* tails, const HyRows& r, cudaStream_t s);
+                         const void* tails, const HyRows& r, cudaStream_t s, int act = 1);
 cudaError_t hy_conv_tails(bool f32, const void* in, int ld_in, int C, int taps, void* tails, const HyRows& r, cudaStream_t s);
 
 struct HyDelta { int heads, kv_heads, dim, vdim; };
@@ -184,6 +196,27 @@ cudaError_t hy_moe_plan(const int32_t* idx, int T, int top, int experts, int32_t
 cudaError_t hy_moe_gather(const void* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, void* out, int max_tiles, cudaStream_t s);
 // x[t] = beta * x[t] + sum over choices (in order) wgt[t,c] * y[dst_of[t*top+c]]
 cudaError_t hy_moe_combine(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W, int T, cudaStream_t s, float beta = 1.f);
+
+// ---- several residual streams joined by learned coefficients (hyper-connections), token shift (hybrid_streams.cu) ----
+// xs [T, n, W] fp32 holds the n residual streams of every row (n = 1: a plain residual).
+// x[t, s] = table[ids[t]] * scale for every stream s
+cudaError_t hy_embed_streams(bool f32, const int32_t* ids, const void* table, float* xs, int T, int W, int vocab, float scale, int n, cudaStream_t s);
+// One pass over the rows, each part optional:
+//  (1) y != null: the sublayer that has just run closes, all streams at once from the old ones: x_t <- sum_s upd_mix[s * n + t] x_s + upd_out[t] y   (y [T, W] fp32)
+//  (2) w != null: the next sublayer's input u = sum_s in[s] x_s, v = u / sqrt(mean(u^2) + eps) * w.  rows != null: row t of the output reads row
+//      rows[t] of xs (the rows whose logits are wanted); then (1) is not allowed.
+//      shift_state == null: v goes to h[t] (activation type, pitch ldh).
+//      shift_state != null (token shift follows): v goes to hn[t] (fp32 [T, W]); the CTA of a sequence's last row also moves the sequence's carried
+//      row shift_state[slot] to prev[seq] and stores v in its place.  hy_token_shift then makes h[t] = v_t + (v_(t-1) - v_t) * mu, with v_(t-1) from
+//      hn, from prev (first row of a step that continues a sequence) or zero (first token).
+struct HyStreams { int n; const float* upd_mix; const float* upd_out; const float* in; };
+cudaError_t hy_stream_norm(bool f32, const HyStreams& c, float* xs, const float* y, const int32_t* rows, const float* w, float eps, void* h, int ldh, float* hn, float* shift_state,
+                           float* prev, const HyRows& r, int T, int W, cudaStream_t s);
+cudaError_t hy_token_shift(bool f32, const float* hn, const float* prev, const float* mu, void* h, int ldh, const HyRows& r, int W, cudaStream_t s);
+// out[t, :n] = in[t, :n] / sqrt(mean(in[t, :n]^2) + eps) * w — RMS norm of a projection's first n columns (fp32 arithmetic, activation type in and out)
+cudaError_t hy_rmsnorm_act(bool f32, const void* in, int ld_in, int n, const float* w, void* out, int ld_out, float eps, int T, cudaStream_t s);
+// x[t, c] *= sigmoid(g[t, c]) for c < n, in place (activation type)
+cudaError_t hy_sigmoid_gate(bool f32, void* x, int ldx, const void* g, int ldg, int n, int T, cudaStream_t s);
 
 cudaError_t hy_gather_rows_f32(const float* x, const int32_t* rows, float* out, int n, int W, cudaStream_t s);
 // softcap > 0: logits <- softcap * tanh(logits / softcap), in place, before the arg-max (ties -> lowest id)

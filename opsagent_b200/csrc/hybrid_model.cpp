@@ -111,13 +111,27 @@ std::vector<float> HybridModel::vec(const std::string& name, int n, float init_m
     return v;
 }
 bool HybridModel::has_tensor(const std::string& name) const { return st_ && st_->st.has(name); }
-int HybridModel::rope_table(float base, int dims) {        // cos / sin of position * base^(-2 i / dims), angles in double, [max_seq_len, dims / 2]
-    for (size_t i = 0; i < ropes_.size(); ++i) if (ropes_[i].base == base && ropes_[i].dims == dims) return (int)i;
-    RopeTable rt; rt.base = base; rt.dims = dims; const int half = dims / 2;
+// cos / sin of position * f_i, f_i = base^(-2 i / dims), angles in double, [max_seq_len, dims / 2].  With YaRN scaling (sc) the frequency is a
+// blend of f_i and f_i / factor along a ramp over i, and both tables carry the amplitude 0.1 ln(factor) + 1.
+int HybridModel::rope_table(float base, int dims, const HyRotScaling* sc) {
+    const HyRotScaling none; const HyRotScaling& k = sc ? *sc : none;
+    for (size_t i = 0; i < ropes_.size(); ++i) {
+        const RopeTable& t = ropes_[i];
+        if (t.base == base && t.dims == dims && t.sc.on == k.on && (!k.on || (t.sc.factor == k.factor && t.sc.original == k.original && t.sc.fast == k.fast && t.sc.slow == k.slow))) return (int)i;
+    }
+    RopeTable rt; rt.base = base; rt.dims = dims; rt.sc = k; const int half = dims / 2;
     std::vector<float> cs((size_t)opt.max_seq_len * std::max(1, half)), sn(cs.size());
+    double amp = 1.0, lo = 0.0, hi = 0.0;
+    if (k.on) {
+        const double pi = 3.14159265358979323846;
+        auto where = [&](double turns) { return dims * std::log((double)k.original / (2.0 * pi * turns)) / (2.0 * std::log((double)base)); };
+        lo = std::max(std::floor(where(k.fast)), 0.0); hi = std::min(std::ceil(where(k.slow)), (double)(dims - 1));
+        amp = 0.1 * std::log((double)k.factor) + 1.0;
+    }
     for (int i = 0; i < half; ++i) {
-        const double f = std::pow((double)base, -2.0 * i / (double)dims);
-        for (int ps = 0; ps < opt.max_seq_len; ++ps) { cs[(size_t)ps * half + i] = (float)std::cos(ps * f); sn[(size_t)ps * half + i] = (float)std::sin(ps * f); }
+        double f = std::pow((double)base, -2.0 * i / (double)dims);
+        if (k.on) { const double ramp = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001))); f = f / k.factor * ramp + f * (1.0 - ramp); }
+        for (int ps = 0; ps < opt.max_seq_len; ++ps) { cs[(size_t)ps * half + i] = (float)(std::cos(ps * f) * amp); sn[(size_t)ps * half + i] = (float)(std::sin(ps * f) * amp); }
     }
     rt.cos = upload_f32(cs); rt.sin = upload_f32(sn); ropes_.push_back(rt);
     return (int)ropes_.size() - 1;
@@ -146,14 +160,24 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     embed_ = upload_act(tensor("embed", V, W).v);
     head_ = upload_mat(tensor("head", V, W));
     final_norm_ = upload_f32(vec("final.norm", W, 1.f, 0.1f));
-    if (hc_.loop_times > 0) { loop_in_ = upload_mat(tensor("loop.in", W, 2 * W)); loop_step_ = upload_f32(vec("loop.step", hc_.loop_times * W, 0.f, 0.1f)); }
+    if (hc_.loop_times > 0 && hc_.loop_reinject) { loop_in_ = upload_mat(tensor("loop.in", W, 2 * W)); loop_step_ = upload_f32(vec("loop.step", hc_.loop_times * W, 0.f, 0.1f)); }
     lw_.resize(hc_.layers.size());
-    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1, max_ffp = 16, max_lat_heads = 1, max_kv = 0, max_Eattn = 8, max_mix2 = 0, max_gates = 0;
+    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1, max_ffp = 16, max_lat_heads = 1, max_kv = 0, max_Eattn = 8, max_mix2 = 0, max_gates = 0, max_cq = 0;
     for (size_t li = 0; li < hc_.layers.size(); ++li) {
         const HyLayer& l = hc_.layers[li]; LayerW& w = lw_[li];
         const std::string p = "l" + std::to_string(li) + ".", mx = p + "mix.";
         w.norm1 = upload_f32(vec(p + "norm1", W, 1.f, 0.1f));
-        if ((hc_.two_norms || hc_.post_norm) && (l.moe.present || (hc_.post_norm && has_tensor(p + "norm2")))) w.norm2 = upload_f32(vec(p + "norm2", W, 1.f, 0.1f));
+        if ((hc_.two_norms || hc_.post_norm || hc_.sequential) && (l.moe.present || (hc_.post_norm && has_tensor(p + "norm2")))) w.norm2 = upload_f32(vec(p + "norm2", W, 1.f, 0.1f));
+        if (hc_.token_shift && (!st_ || has_tensor(p + "shift"))) w.shift = upload_f32(vec(p + "shift", W, 0.5f, 0.5f));
+        if (hc_.sequential && hc_.streams > 0) {
+            const int n = hc_.streams;
+            for (int q = 0; q < (l.moe.present ? 2 : 1); ++q) {
+                const std::string hp = p + (q ? "hc2." : "hc1.");
+                std::vector<float> mixv = vec(hp + "mix", n * n, 0.f, 0.1f);
+                if (!st_) for (int i = 0; i < n; ++i) mixv[(size_t)i * n + i] += 1.f;          // seeded: near the identity
+                w.hc_in[q] = upload_f32(vec(hp + "in", n, 1.f / (float)n, 0.1f / (float)n)); w.hc_mix[q] = upload_f32(mixv); w.hc_out[q] = upload_f32(vec(hp + "out", n, 1.f, 0.1f));
+            }
+        }
         HostMat in; in.K = W; int rows = 0;
         if (l.type == HY_WINDOW_ATTENTION) {
             // fused input projection [q | k | v | gate] (k, v only where the layer fills a cache of its own), each segment on a multiple of 8 rows
@@ -175,6 +199,16 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
             if (l.bias) { bias.resize(up8(rows), 0.f); w.in_bias = upload_f32(bias); w.in_bias_act = upload_act(bias); }
             if (l.qk_norm) { w.q_norm = upload_f32(vec(mx + "q.norm", l.dim, 1.f, 0.1f)); w.k_norm = upload_f32(vec(mx + "k.norm", l.dim, 1.f, 0.1f)); }
             if (l.sink) w.sink = upload_f32(vec(mx + "sink", l.heads, 0.f, 1.f));
+            if (l.out_bias) w.o_bias = upload_f32(vec(mx + "o.b", W, 0.f, 0.1f));
+            if (l.conv > 0) {          // short convolutions on q | k | v: one weight table over the fused projection's columns (padding columns: zero taps)
+                w.conv_ch = up8(rows);
+                std::vector<float> cw((size_t)w.conv_ch * l.conv, 0.f);
+                auto put_conv = [&](const char* nm, int n, int off) { std::vector<float> c = vec(mx + nm + ".conv", n * l.conv, 0.f, 0.5f); std::memcpy(&cw[(size_t)off * l.conv], c.data(), c.size() * 4); };
+                put_conv("q", qd, w.off_a); put_conv("k", kd, w.off_b); put_conv("v", vd, w.off_c);
+                w.conv_w = upload_f32(cw); max_conv = std::max(max_conv, w.conv_ch);
+            }
+            if (l.rot_dims > 0) w.rope = rope_table(l.rot_base, l.rot_dims);
+            if (l.v_rot) w.rope_v = rope_table(l.rot_base, l.vdim);
             if (l.maps == 2) {        // lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff: one number per layer, fp32
                 const float sp = 1.0f / std::sqrt((float)l.dim);
                 std::vector<float> q1 = vec(mx + "lq1", l.dim, 0.f, sp), k1 = vec(mx + "lk1", l.dim, 0.f, sp), q2 = vec(mx + "lq2", l.dim, 0.f, sp), k2 = vec(mx + "lk2", l.dim, 0.f, sp);
@@ -235,9 +269,18 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
             max_dec = std::max(max_dec, n.kind == HY_LIN_CHANNEL_DECAY ? qk : n.heads); max_h = std::max(max_h, n.heads);
         } else if (l.type == HY_LATENT_ATTENTION) {
             const int qd = l.heads * (l.dim + l.rot_dim), E = l.kv_rank + l.rot_dim;
-            append_rows(in.v, rows, W, tensor(mx + "q", qd, W).v, qd, 1); w.off_a = 0;
+            if (l.q_rank > 0) {        // queries through a latent: [dq | dkv (| g)] in the fused projection, W_uq as a second stage after the latent's norm
+                append_rows(in.v, rows, W, tensor(mx + "dq", l.q_rank, W).v, l.q_rank, 1); w.off_a = 0;
+                w.dq_norm = upload_f32(vec(mx + "dq.norm", l.q_rank, 1.f, 0.1f)); w.uq = upload_mat(tensor(mx + "uq", qd, l.q_rank));
+                max_cq = std::max(max_cq, up8(l.q_rank)); max_p2 = std::max(max_p2, up8(qd));
+            } else { append_rows(in.v, rows, W, tensor(mx + "q", qd, W).v, qd, 1); w.off_a = 0; }
             while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
             w.off_b = rows; append_rows(in.v, rows, W, tensor(mx + "dkv", E, W).v, E, 1);
+            if (l.gate == HY_GATE_CHANNEL) {
+                while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
+                w.off_d = rows; append_rows(in.v, rows, W, tensor(mx + "g", l.heads * l.vdim, W).v, l.heads * l.vdim, 1);
+            }
+            if (l.sink) w.sink = upload_f32(vec(mx + "sink", l.heads, 0.f, 1.f));
             w.dkv_norm = upload_f32(vec(mx + "dkv.norm", l.kv_rank, 1.f, 0.1f));
             // W_uk per head transposed to [rank, dim]: the absorbed query W_uk^T q is then an ordinary A . B^T product
             HostMat uk = tensor(mx + "uk", l.heads * l.dim, l.kv_rank);
@@ -247,7 +290,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
             w.uk_t = upload_act(ukt);
             HostMat uvm = tensor(mx + "uv", l.heads * l.vdim, l.kv_rank);
             w.uv = upload_act(uvm.v);
-            if (!f32_ && opt.hy_tensor_core && opt.hy_unabsorbed_rows > 0 && hy_mha_prefill_supported(HyLatentAttn{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale})) {
+            if (!f32_ && opt.hy_tensor_core && opt.hy_unabsorbed_rows > 0 && hy_mha_prefill_supported(latent_params(l, w))) {
                 HostMat kvu; kvu.N = l.heads * (l.dim + l.vdim); kvu.K = l.kv_rank; kvu.v = uk.v; kvu.v.insert(kvu.v.end(), uvm.v.begin(), uvm.v.end());
                 w.kv_up = upload_mat(kvu);       // [W_uk ; W_uv]: keys and values of a whole context in one product (prefill form)
                 max_kv = std::max(max_kv, up8(kvu.N));
@@ -265,7 +308,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
                 }
                 if (!all) { w.uk_heads.clear(); w.uv_heads.clear(); }
             }
-            w.rope = rope_table(l.rot_base, l.rot_dims);
+            w.rope = rope_table(l.rot_base, l.rot_dims, l.rot_scaling.on ? &l.rot_scaling : nullptr);
             max_Eattn = std::max(max_Eattn, E); max_lat_heads = std::max(max_lat_heads, l.heads); max_qabs = std::max(max_qabs, l.heads * E); max_lat = std::max(max_lat, l.heads * l.kv_rank); max_mix = std::max(max_mix, l.heads * l.vdim);
         } else if (l.type == HY_CHANNEL_DELTA) {
             const int qk = l.kv_heads * l.dim, vd = l.heads * l.vdim;
@@ -387,6 +430,13 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         n_tiles_ = (int32_t*)dmalloc((size_t)(4 + 2 * max_E) * 4); dst_of_ = (int32_t*)dmalloc(MR * max_top * 4);
     }
     if (hc_.post_norm) { y_ = (float*)dmalloc(MR * W * 4); y2_ = (float*)dmalloc(MR * W * 4); }
+    if (hc_.sequential) {
+        n_streams_ = std::max(1, hc_.streams);
+        y_ = (float*)dmalloc(MR * W * 4); xs_ = (float*)dmalloc(MR * n_streams_ * W * 4);
+        ones_ = upload_f32(std::vector<float>(64, 1.f));
+        if (hc_.token_shift) { hn_ = (float*)dmalloc(MR * W * 4); shift_prev_ = (float*)dmalloc((size_t)opt.max_batch * W * 4); }
+        if (max_cq > 0) { ld_cq_ = max_cq; cq_ = dmalloc(MR * ld_cq_ * es_); }
+    }
     if (max_mix2 > 0) { ld_mix2_ = up8(max_mix2); mix2_ = dmalloc(MR * ld_mix2_ * es_); }
     if (max_gates > 0) {
         ld_gates_ = max_gates; gates_ = (float*)dmalloc(MR * ld_gates_ * 4);
@@ -411,7 +461,8 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     max_pages_per_seq = opt.max_seq_len / 64;
     if (num_pages < 1) throw std::runtime_error("cache pool too small");
     caches_.resize(hc_.n_caches); states_.resize(hc_.n_states); tails_.resize(hc_.n_states); aux_.resize(hc_.n_states);
-    state_slots = hc_.n_states > 0 ? opt.max_batch : 0;
+    state_slots = (hc_.n_states > 0 || hc_.token_shift) ? opt.max_batch : 0;
+    if (hc_.token_shift) { shift_states_.resize(hc_.runs.size()); for (size_t i = 0; i < hc_.runs.size(); ++i) shift_states_[i] = (float*)dmalloc((size_t)state_slots * W * 4); }
     for (const HyRun& r : hc_.runs) {
         const HyLayer& l = hc_.layers[r.layer];
         if (r.cache_owner) { const size_t b = (size_t)num_pages * 64 * cache_row_width(l) * es_; caches_[r.cache_idx] = dmalloc(b); kv_pool_bytes += b; }
@@ -419,6 +470,8 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
             const HyLinear& n = l.lin;
             states_[r.state_idx] = (float*)dmalloc((size_t)state_slots * n.heads * n.dim * n.vdim * 4);
             if (n.kind == HY_LIN_MATRIX_MEMORY) aux_[r.state_idx] = (float*)dmalloc((size_t)state_slots * n.heads * (n.dim + 1) * 4);
+        } else if (r.state_idx >= 0 && l.type == HY_WINDOW_ATTENTION) {
+            tails_[r.state_idx] = dmalloc((size_t)state_slots * std::max(1, l.conv - 1) * lw_[r.layer].conv_ch * es_);          // the convolutions' last inputs
         } else if (r.state_idx >= 0) {
             const int sd = l.type == HY_CHANNEL_DELTA ? l.dim : l.state;
             states_[r.state_idx] = (float*)dmalloc((size_t)state_slots * l.heads * sd * l.vdim * 4);
@@ -480,7 +533,7 @@ void HybridModel::moe(const LayerW& w, const HyLayer& l, const void* h_in, const
     const HyMoe& m = l.moe; const int W = hc_.width, T = r.T;
     const bool relu2 = m.act == HY_EXPERT_RELU2; const int rows1 = relu2 ? w.ffp : 2 * w.ffp;
     if (m.dense) {        // one feed-forward for every row: up product with the activation in its epilogue, down product into the sublayer's fp32 output
-        gemm(HY_STORE, h_in, Wld_, w.up, act_, up8(m.ff), T, nullptr, 1.f, nullptr, relu2 ? 1 : 0); MARK(25);
+        gemm(HY_STORE, h_in, Wld_, w.up, act_, up8(m.ff), T, nullptr, 1.f, nullptr, relu2 ? 1 : m.act == HY_EXPERT_GELU_TANH ? 2 : 0); MARK(25);
         gemm(HY_STORE_F32, act_, up8(m.ff), w.dn, y_, W, T, nullptr, 1.f); MARK(26);
         return;
     }
@@ -529,6 +582,7 @@ const char* HybridModel::kt_name(int id) const {
 static HyWinAttn win_params(const HyLayer& l, float lambda) {
     HyWinAttn a{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, lambda, 1.f - l.diff};
     a.softcap = l.softcap; a.slope_exp = l.slope_exp; a.q_temp_coef = l.q_temp_coef; a.q_temp_every = l.q_temp_every;
+    a.out_rot = l.v_rot ? (l.rot_layout == HY_ROT_HALVES ? 2 : 1) : 0;
     return a;
 }
 
@@ -559,6 +613,122 @@ void HybridModel::linear_mixer(const HyRun& run, const HyLayer& l, const LayerW&
     }
 }
 
+
+HyLatentAttn HybridModel::latent_params(const HyLayer& l, const LayerW& w) const {
+    HyLatentAttn a{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale};
+    a.window = l.type == HY_LATENT_ATTENTION ? l.window : 0; a.rot_layout = l.rot_layout; a.sink = w.sink;
+    return a;
+}
+
+void HybridModel::window_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& MARK, void* q, void* k, void* v, int ld,
+                               const void* gate, int ldg) {
+    HyWinAttn a{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, w.lambda, 1.f - l.diff};
+    if (l.v_rot) { a.out_rot = l.rot_layout == HY_ROT_HALVES ? 2 : 1; a.out_cos = ropes_[w.rope_v].cos; a.out_sin = ropes_[w.rope_v].sin; }
+    if (l.rot_dims > 0 || l.v_rot) {
+        const HyRotary rot{l.rot_dims, l.rot_layout, l.rot_dims > 0 ? ropes_[w.rope].cos : nullptr, l.rot_dims > 0 ? ropes_[w.rope].sin : nullptr,
+                           l.v_rot ? ropes_[w.rope_v].cos : nullptr, l.v_rot ? ropes_[w.rope_v].sin : nullptr};
+        cuda_check(hy_win_rope_prep(f32_, a, rot, q, ld, k, v, ld, caches_[run.cache_idx], r, stream), "rotary + cache write");
+    } else cuda_check(hy_win_prep(f32_, a, q, ld, k, v, ld, w.q_norm, w.k_norm, hc_.eps, caches_[run.cache_idx], r, stream), "query / key norm + cache write");
+    MARK(23);
+    if (tl.mma) {
+        cuda_check(hy_win_attention_mma(a, q, ld, caches_[run.cache_idx], w.sink, gate, ldg, mix_, ld_mix_, hc_.eps, r, d_meta_ + tl.o_wseq, d_meta_ + tl.o_wq0, tl.n_w, stream), "windowed attention (mma)");
+        cuda_check(hy_win_decode_mma(a, q, ld, caches_[run.cache_idx], w.sink, gate, ldg, mix_, ld_mix_, hc_.eps, r, d_meta_ + tl.o_dseq, d_meta_ + tl.o_dq0, tl.n_d, stream), "windowed attention (mma, decoding rows)");
+    } else cuda_check(hy_win_attention(f32_, a, q, ld, caches_[run.cache_idx], w.sink, gate, ldg, mix_, ld_mix_, hc_.eps, r, stream), "windowed attention");
+    MARK(24);
+}
+
+void HybridModel::latent_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& MARK, void* q, int ldq, void* ckv, int ldc) {
+    auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
+    const int T = r.T;
+    const HyLatentAttn a = latent_params(l, w);
+    const int E = l.kv_rank + l.rot_dim;
+    cuda_check(hy_mla_prep(f32_, a, q, ldq, ckv, ldc, w.dkv_norm, hc_.eps, ropes_[w.rope].cos, ropes_[w.rope].sin, caches_[run.cache_idx], q_abs_, r, stream), "latent cache write"); MARK(4);
+    if (tl.any_small) {
+        // absorbed queries: q_abs[t, h, :rank] = W_uk[h]^T q_unrotated[t, h]
+        const bool head_tc = !w.uk_heads.empty() && T >= 256 && ldq % 8 == 0;      // prefill-sized steps: one tcgen05 GEMM per head; smaller ones: one batched launch
+        if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE_F32, at(q, (size_t)hd * (l.dim + l.rot_dim)), ldq, w.uk_heads[hd], q_abs_ + (size_t)hd * E, l.heads * E, T, nullptr, 1.f);
+        else cuda_check(hy_gemm(f32_, HY_STORE_F32, q, ldq, w.uk_t, l.dim, q_abs_, l.heads * E, T, l.kv_rank, l.dim, nullptr, 1.f, l.heads,
+                                l.dim + l.rot_dim, (long long)l.kv_rank * l.dim, E, stream), "query absorption");
+        MARK(3);
+        if (tl.mma) {
+            HyMlaSplit sp{nullptr, nullptr, nullptr, split_o_, split_ml_};
+            if (tl.n_merge > 0) { sp.tile_k0 = d_meta_ + tl.o_k0; sp.tile_k1 = d_meta_ + tl.o_k1; sp.tile_slot = d_meta_ + tl.o_slot; }
+            cuda_check(hy_mla_attention_mma(a, q_abs_, caches_[run.cache_idx], lat_, r, d_meta_ + tl.o_seq, d_meta_ + tl.o_q0, tl.n, sp, stream), "latent attention (mma)");
+            cuda_check(hy_mla_merge(d_meta_ + tl.o_mrow, d_meta_ + tl.o_mslot, d_meta_ + tl.o_mparts, tl.n_merge, split_o_, split_ml_, lat_, l.heads, l.kv_rank, stream, a.sink), "latent attention (join)");
+        } else cuda_check(hy_mla_attention(f32_, a, q_abs_, caches_[run.cache_idx], lat_, r, stream), "latent attention");
+        MARK(5);
+        if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE, at(lat_, (size_t)hd * l.kv_rank), l.heads * l.kv_rank, w.uv_heads[hd], at(mix_, (size_t)hd * l.vdim), ld_mix_, T, nullptr, 1.f);
+        else cuda_check(hy_gemm(f32_, HY_STORE, lat_, l.heads * l.kv_rank, w.uv, l.kv_rank, mix_, ld_mix_, T, l.vdim, l.kv_rank, nullptr, 1.f, l.heads, l.kv_rank,
+                                (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection");
+        MARK(3);
+    }
+    if (tl.n_ptiles > 0) {      // prefill form for the sequences that bring many rows (after the absorbed path, whose up-projection wrote every row of mix_)
+        cuda_check(hy_gather_ctx(caches_[run.cache_idx], E, r, d_meta_ + tl.o_base, tl.max_ctx, lat_ctx_, stream), "context gather");
+        gemm(HY_STORE, lat_ctx_, E, w.kv_up, kv_ctx_, ld_kv_, tl.ctx_rows, nullptr, 1.f); MARK(20);
+        cuda_check(hy_mha_prefill(a, q, ldq, q_abs_, kv_ctx_, ld_kv_, lat_ctx_, mix_, ld_mix_, r, d_meta_ + tl.o_pseq, d_meta_ + tl.o_phead,
+                                  d_meta_ + tl.o_prow0, d_meta_ + tl.o_base, tl.n_ptiles, stream), "attention (prefill form)"); MARK(21);
+    }
+}
+
+// Designs whose sublayers run in sequence on pre-norms of the residual they find: per layer execution
+//   [close the previous sublayer + open the mixer: streams' update, u = in . x, RMS norm] -> token shift -> input projection -> mixer -> output
+//   projection (fp32 y) -> [close the mixer + open the feed-forward] -> up product with the activation -> down product (fp32 y).
+// A sublayer's y is folded into the streams by the kernel that opens the next sublayer, so a layer costs two passes over the residual.
+void HybridModel::forward_sequential(const HyRows& r, const std::vector<TileList>& tile_lists, const int32_t* d_tokens, const std::function<void(int)>& MARK) {
+    auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
+    const int T = r.T, W = hc_.width, n = n_streams_;
+    const bool hyper = hc_.streams > 0;
+    const float *pend_mix = nullptr, *pend_out = nullptr;      // coefficients of the sublayer whose y_ has not been folded into the streams yet
+    bool pending = false;
+    auto open = [&](const float* in, const float* norm_w, float* shift_state, const char* what) {
+        const HyStreams c{n, pend_mix, pend_out, in};
+        cuda_check(hy_stream_norm(f32_, c, xs_, pending ? y_ : nullptr, nullptr, norm_w, hc_.eps, h_, Wld_, hn_, shift_state, shift_prev_, r, T, W, stream), what);
+        pending = false;
+    };
+    for (const HyRun& run : hc_.runs) {
+        const HyLayer& l = hc_.layers[run.layer]; const LayerW& w = lw_[run.layer];
+        float* sstate = w.shift ? shift_states_[run.index] : nullptr;
+        open(hyper ? w.hc_in[0] : ones_, w.norm1, sstate, "streams + norm (mixer)");
+        if (sstate) cuda_check(hy_token_shift(f32_, hn_, shift_prev_, w.shift, h_, Wld_, r, W, stream), "token shift");
+        MARK(22);
+        gemm(HY_STORE, h_, Wld_, w.in, proj_, ld_proj_, T, w.in_bias, 1.f, w.in_bias_act); MARK(2);
+        if (l.type == HY_LATENT_ATTENTION) {
+            void* q = at(proj_, w.off_a); int ldq = ld_proj_;
+            if (l.q_rank > 0) {
+                cuda_check(hy_rmsnorm_act(f32_, at(proj_, w.off_a), ld_proj_, l.q_rank, w.dq_norm, cq_, ld_cq_, hc_.eps, T, stream), "query latent norm");
+                gemm(HY_STORE, cq_, ld_cq_, w.uq, p2_, ld_p2_, T, nullptr, 1.f); MARK(10);
+                q = p2_; ldq = ld_p2_;
+            }
+            latent_mixer(run, l, w, r, tile_lists[run.layer], MARK, q, ldq, at(proj_, w.off_b), ld_proj_);
+            if (l.gate == HY_GATE_CHANNEL) { cuda_check(hy_sigmoid_gate(f32_, mix_, ld_mix_, at(proj_, w.off_d), ld_proj_, l.heads * l.vdim, T, stream), "output gate"); MARK(9); }
+        } else if (l.type == HY_WINDOW_ATTENTION) {
+            void* src = proj_; int ld = ld_proj_;
+            if (l.conv > 0) {
+                cuda_check(hy_conv_silu(f32_, proj_, ld_proj_, w.conv_ch, w.conv_w, nullptr, l.conv, conv_, ld_conv_, tails_[run.state_idx >= 0 ? run.state_idx : 0], r, stream, 0), "conv");
+                if (l.conv > 1) cuda_check(hy_conv_tails(f32_, proj_, ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails");
+                MARK(6); src = conv_; ld = ld_conv_;
+            }
+            window_mixer(run, l, w, r, tile_lists[run.layer], MARK, at(src, w.off_a), at(src, w.off_b), at(src, w.off_c), ld, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_);
+        } else throw std::runtime_error("forward: this design has no such mixer");
+        gemm(HY_STORE_F32, mix_, ld_mix_, w.o, y_, W, T, w.o_bias, 1.f); MARK(11);
+        pending = true; pend_mix = hyper ? w.hc_mix[0] : ones_; pend_out = hyper ? w.hc_out[0] : ones_;
+        if (l.moe.present) {
+            open(hyper ? w.hc_in[1] : ones_, w.norm2, nullptr, "streams + norm (feed-forward)"); MARK(22);
+            moe(w, l, h_, r, MARK, d_tokens);
+            pending = true; pend_mix = hyper ? w.hc_mix[1] : ones_; pend_out = hyper ? w.hc_out[1] : ones_;
+        }
+        if (capture_layers) {          // debug: the residual (sum of the streams) after this execution
+            open(nullptr, nullptr, nullptr, "streams (capture)");
+            cuda_check(cudaStreamSynchronize(stream), "capture sync");
+            std::vector<float> tmp((size_t)T * n * W);
+            cuda_check(cudaMemcpy(tmp.data(), xs_, tmp.size() * 4, cudaMemcpyDeviceToHost), "capture D2H");
+            const size_t n0 = capture_layers->size(); capture_layers->resize(n0 + (size_t)T * W, 0.f);
+            for (int t = 0; t < T; ++t) for (int sidx = 0; sidx < n; ++sidx) for (int c = 0; c < W; ++c) (*capture_layers)[n0 + (size_t)t * W + c] += tmp[((size_t)t * n + sidx) * W + c];
+        }
+    }
+    if (pending) open(nullptr, nullptr, nullptr, "streams (last sublayer)");
+}
+
 void HybridModel::forward(const StepInput& in, float* logits_out) {
     const int T = (int)in.tokens.size(), S = in.n_seqs, NS = (int)in.sample_rows.size(), W = hc_.width, V = hc_.vocab;
     if (T <= 0 || T > MR_ || NS > MS_ || S <= 0 || S > opt.max_batch) throw std::runtime_error("forward: bad batch size");
@@ -585,9 +755,6 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     // attention plans, one per attention layer.  Sequences that bring at least hy_unabsorbed_rows rows take the prefill form (keys / values of
     // their context up-projected by a GEMM, ordinary multi-head attention); the others — decoding rows, short portions — the absorbed form:
     // tiles of 64 consecutive (row, head) pairs of one sequence, a decoding row with a long context cut into parts.
-    struct TileList { bool mma = false, any_small = false; size_t o_seq = 0, o_q0 = 0, o_k0 = 0, o_k1 = 0, o_slot = 0, o_mrow = 0, o_mslot = 0, o_mparts = 0; int n = 0, n_merge = 0;
-                      size_t o_pseq = 0, o_phead = 0, o_prow0 = 0, o_base = 0; int n_ptiles = 0, ctx_rows = 0, max_ctx = 0;
-                      size_t o_wseq = 0, o_wq0 = 0, o_dseq = 0, o_dq0 = 0; int n_w = 0, n_d = 0; };
     std::vector<TileList> tile_lists(hc_.layers.size());
     for (size_t li = 0; li < hc_.layers.size(); ++li) {
         const HyLayer& l = hc_.layers[li]; TileList& tl = tile_lists[li];
@@ -608,7 +775,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
         }
         if (l.type != HY_LATENT_ATTENTION) continue;
         const bool prefill_form = lw_[li].kv_up.tc && kv_ctx_;
-        tl.mma = !f32_ && opt.hy_tensor_core && hy_mla_mma_supported(HyLatentAttn{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale});
+        tl.mma = !f32_ && opt.hy_tensor_core && hy_mla_mma_supported(latent_params(l, lw_[li]));
         tile_seq_.clear(); tile_q0_.clear(); tile_k0_.clear(); tile_k1_.clear(); tile_slot_.clear(); merge_row_.clear(); merge_slot_.clear(); merge_parts_.clear();
         ptile_seq_.clear(); ptile_head_.clear(); ptile_row0_.clear(); seq_base_.assign(S, -1);
         int next_slot = 0;
@@ -622,16 +789,16 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             }
             tl.any_small = true;
             if (!tl.mma) continue;
-            const int ctx = seq_pos0_[sq] + 1;
+            const int ctx = seq_pos0_[sq] + 1, vis0 = l.window > 0 ? std::max(0, ctx - l.window) / 32 * 32 : 0;       // first visible cache row of a decoding row, on a tile border
             // a decoding row with a long context: its cache rows in 2..16 parts of >= 256 rows, one CTA each, joined afterwards.  The cut
             // depends on the row's position only.
-            int parts = (len == 1 && nq <= HY_MLA_TILE_QUERIES) ? std::min(16, ctx / 256) : 1;
+            int parts = (len == 1 && nq <= HY_MLA_TILE_QUERIES) ? std::min(16, (ctx - vis0) / 256) : 1;
             if (parts > 1 && next_slot + parts > split_slots_) parts = 1;
             if (parts > 1) {
-                const int per = ((ctx + parts - 1) / parts + 31) / 32 * 32; parts = (ctx + per - 1) / per;
+                const int per = ((ctx - vis0 + parts - 1) / parts + 31) / 32 * 32; parts = (ctx - vis0 + per - 1) / per;
                 merge_row_.push_back(in.seq_row0[sq]); merge_slot_.push_back(next_slot); merge_parts_.push_back(parts);
                 for (int pz = 0; pz < parts; ++pz) {
-                    tile_seq_.push_back(sq); tile_q0_.push_back(0); tile_k0_.push_back(pz * per); tile_k1_.push_back(std::min(ctx, (pz + 1) * per)); tile_slot_.push_back(next_slot++);
+                    tile_seq_.push_back(sq); tile_q0_.push_back(0); tile_k0_.push_back(vis0 + pz * per); tile_k1_.push_back(std::min(ctx, vis0 + (pz + 1) * per)); tile_slot_.push_back(next_slot++);
                 }
                 continue;
             }
@@ -661,9 +828,11 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
         cudaEventRecord(ev_all[ek++], stream);
     }
     const std::function<void(int)> MARK = [&](int id) { if (profile_all && ek < ev_all.size()) { ev_ids[ek] = id; cudaEventRecord(ev_all[ek++], stream); } };
-    cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, hc_.loop_times > 0 ? x0_ : nullptr, T, W, V, hc_.embed_scale, stream, hc_.post_norm ? h_ : nullptr, Wld_), "embed"); MARK(0);
+    if (hc_.sequential) { cuda_check(hy_embed_streams(f32_, d_meta_ + o_tok, embed_, xs_, T, W, V, hc_.embed_scale, n_streams_, stream), "embed"); MARK(0); forward_sequential(r, tile_lists, d_meta_ + o_tok, MARK); }
+    else { cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, hc_.loop_times > 0 ? x0_ : nullptr, T, W, V, hc_.embed_scale, stream, hc_.post_norm ? h_ : nullptr, Wld_), "embed"); MARK(0); }
     auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
     for (const HyRun& run : hc_.runs) {
+        if (hc_.sequential) break;
         const HyLayer& l = hc_.layers[run.layer]; const LayerW& w = lw_[run.layer];
         if (run.first_of_pass) {         // re-injection: x <- W_in [x ; x0] + step[pass]
             cuda_check(hy_concat(f32_, x_, x0_, cat_, T, W, stream), "concat");
@@ -711,50 +880,10 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
         else { cuda_check(hy_layernorm(f32_, x_, nullptr, w.norm1, h_, Wld_, T, W, hc_.eps, stream), "layer norm"); MARK(1); }
         gemm(HY_STORE, h_, Wld_, w.in, proj_, ld_proj_, T, w.in_bias, 1.f, w.in_bias_act); MARK(2);
         if (l.type == HY_WINDOW_ATTENTION) {
-            const HyWinAttn a{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, w.lambda, 1.f - l.diff};
             const bool own = run.cache_owner;
-            cuda_check(hy_win_prep(f32_, a, at(proj_, w.off_a), ld_proj_, own ? at(proj_, w.off_b) : nullptr, own ? at(proj_, w.off_c) : nullptr, ld_proj_, w.q_norm, w.k_norm, hc_.eps,
-                                   caches_[run.cache_idx], r, stream), "query / key norm + cache write"); MARK(23);
-            const TileList& tl = tile_lists[run.layer];
-            if (tl.mma) {
-                cuda_check(hy_win_attention_mma(a, at(proj_, w.off_a), ld_proj_, caches_[run.cache_idx], w.sink, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, mix_, ld_mix_,
-                                                hc_.eps, r, d_meta_ + tl.o_wseq, d_meta_ + tl.o_wq0, tl.n_w, stream), "windowed attention (mma)");
-                cuda_check(hy_win_decode_mma(a, at(proj_, w.off_a), ld_proj_, caches_[run.cache_idx], w.sink, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, mix_, ld_mix_,
-                                             hc_.eps, r, d_meta_ + tl.o_dseq, d_meta_ + tl.o_dq0, tl.n_d, stream), "windowed attention (mma, decoding rows)");
-            } else cuda_check(hy_win_attention(f32_, a, at(proj_, w.off_a), ld_proj_, caches_[run.cache_idx], w.sink, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, mix_, ld_mix_, hc_.eps,
-                                             r, stream), "windowed attention");
-            MARK(24);
+            window_mixer(run, l, w, r, tile_lists[run.layer], MARK, at(proj_, w.off_a), own ? at(proj_, w.off_b) : nullptr, own ? at(proj_, w.off_c) : nullptr, ld_proj_, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_);
         } else if (l.type == HY_LATENT_ATTENTION) {
-            const HyLatentAttn a{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale};
-            const int E = l.kv_rank + l.rot_dim;
-            const TileList& tl = tile_lists[run.layer];
-            cuda_check(hy_mla_prep(f32_, a, at(proj_, w.off_a), ld_proj_, at(proj_, w.off_b), ld_proj_, w.dkv_norm, hc_.eps, ropes_[w.rope].cos, ropes_[w.rope].sin,
-                                   caches_[run.cache_idx], q_abs_, r, stream), "latent cache write"); MARK(4);
-            if (tl.any_small) {
-                // absorbed queries: q_abs[t, h, :rank] = W_uk[h]^T q_unrotated[t, h]
-                const bool head_tc = !w.uk_heads.empty() && T >= 256;      // prefill-sized steps: one tcgen05 GEMM per head; smaller ones: one batched launch
-                if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE_F32, at(proj_, w.off_a + (size_t)hd * (l.dim + l.rot_dim)), ld_proj_, w.uk_heads[hd], q_abs_ + (size_t)hd * E, l.heads * E, T, nullptr, 1.f);
-                else cuda_check(hy_gemm(f32_, HY_STORE_F32, at(proj_, w.off_a), ld_proj_, w.uk_t, l.dim, q_abs_, l.heads * E, T, l.kv_rank, l.dim, nullptr, 1.f, l.heads,
-                                        l.dim + l.rot_dim, (long long)l.kv_rank * l.dim, E, stream), "query absorption");
-                MARK(3);
-                if (tl.mma) {
-                    HyMlaSplit sp{nullptr, nullptr, nullptr, split_o_, split_ml_};
-                    if (tl.n_merge > 0) { sp.tile_k0 = d_meta_ + tl.o_k0; sp.tile_k1 = d_meta_ + tl.o_k1; sp.tile_slot = d_meta_ + tl.o_slot; }
-                    cuda_check(hy_mla_attention_mma(a, q_abs_, caches_[run.cache_idx], lat_, r, d_meta_ + tl.o_seq, d_meta_ + tl.o_q0, tl.n, sp, stream), "latent attention (mma)");
-                    cuda_check(hy_mla_merge(d_meta_ + tl.o_mrow, d_meta_ + tl.o_mslot, d_meta_ + tl.o_mparts, tl.n_merge, split_o_, split_ml_, lat_, l.heads, l.kv_rank, stream), "latent attention (join)");
-                } else cuda_check(hy_mla_attention(f32_, a, q_abs_, caches_[run.cache_idx], lat_, r, stream), "latent attention");
-                MARK(5);
-                if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE, at(lat_, (size_t)hd * l.kv_rank), l.heads * l.kv_rank, w.uv_heads[hd], at(mix_, (size_t)hd * l.vdim), ld_mix_, T, nullptr, 1.f);
-                else cuda_check(hy_gemm(f32_, HY_STORE, lat_, l.heads * l.kv_rank, w.uv, l.kv_rank, mix_, ld_mix_, T, l.vdim, l.kv_rank, nullptr, 1.f, l.heads, l.kv_rank,
-                                        (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection");
-                MARK(3);
-            }
-            if (tl.n_ptiles > 0) {      // prefill form for the sequences that bring many rows (after the absorbed path, whose up-projection wrote every row of mix_)
-                cuda_check(hy_gather_ctx(caches_[run.cache_idx], E, r, d_meta_ + tl.o_base, tl.max_ctx, lat_ctx_, stream), "context gather");
-                gemm(HY_STORE, lat_ctx_, E, w.kv_up, kv_ctx_, ld_kv_, tl.ctx_rows, nullptr, 1.f); MARK(20);
-                cuda_check(hy_mha_prefill(a, at(proj_, w.off_a), ld_proj_, q_abs_, kv_ctx_, ld_kv_, lat_ctx_, mix_, ld_mix_, r, d_meta_ + tl.o_pseq, d_meta_ + tl.o_phead,
-                                          d_meta_ + tl.o_prow0, d_meta_ + tl.o_base, tl.n_ptiles, stream), "attention (prefill form)"); MARK(21);
-            }
+            latent_mixer(run, l, w, r, tile_lists[run.layer], MARK, at(proj_, w.off_a), ld_proj_, at(proj_, w.off_b), ld_proj_);
         } else if (l.type == HY_CHANNEL_DELTA) {
             const HyDelta d{l.heads, l.kv_heads, l.dim, l.vdim};
             cuda_check(hy_conv_silu(f32_, at(proj_, w.off_a), ld_proj_, w.conv_ch, w.conv_w, nullptr, l.conv, conv_, ld_conv_, tails_[run.state_idx], r, stream), "conv");
@@ -788,7 +917,10 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
         capture_layers = nullptr;
     }
     if (NS > 0) {
-        if (hc_.norm == HY_RMS_NORM) cuda_check(hy_rmsnorm_pair(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, nullptr, nullptr, Wld_, NS, W, hc_.eps, stream), "final norm");
+        if (hc_.sequential) {      // x = the sum of the streams, of the wanted rows only
+            const HyStreams fin{n_streams_, nullptr, nullptr, ones_};
+            cuda_check(hy_stream_norm(f32_, fin, xs_, nullptr, d_meta_ + o_samp, final_norm_, hc_.eps, hs_, Wld_, nullptr, nullptr, nullptr, r, NS, W, stream), "final norm");
+        } else if (hc_.norm == HY_RMS_NORM) cuda_check(hy_rmsnorm_pair(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, nullptr, nullptr, Wld_, NS, W, hc_.eps, stream), "final norm");
         else cuda_check(hy_layernorm(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, Wld_, NS, W, hc_.eps, stream), "final norm");
         if (!logits_out && NS > opt.max_batch) throw std::runtime_error("forward: more sampled rows than sequences need a caller's logits buffer");
         float* lg = logits_out ? logits_out : logits_;

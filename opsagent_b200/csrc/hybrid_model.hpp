@@ -3,7 +3,8 @@
 // tokens alike), attention layers keep their compressed keys (latent attention) or their keys and values (windowed attention) in the engine's
 // 64-token pages, recurrent layers keep an fp32 state and their convolution tails (or, for a matrix memory, its normaliser and running
 // maximum) in the sequence's state slot.  Designs whose norm follows the sum (x <- norm(alpha x + sublayer(x))) run mixer and feed-forward in
-// sequence; the others run them side by side on norms of the same residual.
+// sequence; pre-norm designs run them either side by side on norms of the same residual or in sequence, the latter optionally on several
+// residual streams (hyper-connections) and with a token shift in front of the mixer whose carried row lives in the state slot too.
 #pragma once
 #include <functional>
 #include <string>
@@ -47,12 +48,19 @@ private:
         int n_exp = 0, n_top = 0, ff_max = 0;         // experts and choices per token as the kernels see them (a shared expert is one more expert that every token chooses)
         int32_t* table = nullptr; void* shared_gate = nullptr;                               // router by token id; gate row of the shared expert
         Mat up, dn;                                   // dense feed-forward
+        // designs with sublayers in sequence: token shift weight, hyper-connection coefficients of the mixer (1) and the feed-forward (2), all fp32 on the device
+        float *shift = nullptr, *hc_in[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *o_bias = nullptr;
+        Mat uq; float* dq_norm = nullptr; int rope_v = -1;      // latent attention with a low-rank query; rotary table of rotated values
         // linear attention and attention beside a matrix memory: segments of the fused input projection, second stage and biases
         int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_a1 = 0, off_lq = 0, off_lk = 0, off_lv = 0;
         float *a2_bias = nullptr, *decay = nullptr, *o2_bias = nullptr, *out_w1 = nullptr, *out_w2 = nullptr, *gates_bias = nullptr;
         Mat o2, gates;                                // output projection of the attention side; [W_i ; W_f] of the matrix memory (fp32 out)
     };
-    struct RopeTable { float base; int dims; float *cos = nullptr, *sin = nullptr; };
+    struct RopeTable { float base; int dims; HyRotScaling sc; float *cos = nullptr, *sin = nullptr; };
+    // per-step plan of one attention layer: offsets (in words) of its tile lists in the step's metadata arena
+    struct TileList { bool mma = false, any_small = false; size_t o_seq = 0, o_q0 = 0, o_k0 = 0, o_k1 = 0, o_slot = 0, o_mrow = 0, o_mslot = 0, o_mparts = 0; int n = 0, n_merge = 0;
+                      size_t o_pseq = 0, o_phead = 0, o_prow0 = 0, o_base = 0; int n_ptiles = 0, ctx_rows = 0, max_ctx = 0;
+                      size_t o_wseq = 0, o_wq0 = 0, o_dseq = 0, o_dq0 = 0; int n_w = 0, n_d = 0; };
 
     void* dmalloc(size_t bytes);
     float* upload_f32(const std::vector<float>& v);
@@ -63,7 +71,14 @@ private:
     void gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha, const void* bias_act = nullptr, int act = 0);
     // routed experts (and a dense feed-forward): x = beta x + sum of the chosen experts' outputs
     void moe(const LayerW& w, const HyLayer& l, const void* h, const HyRows& r, const std::function<void(int)>& mark, const int32_t* tokens = nullptr, float beta = 1.f);
-    int rope_table(float base, int dims);
+    int rope_table(float base, int dims, const HyRotScaling* sc = nullptr);
+    // latent attention of one layer execution: q [T, ldq] (head by head [dim | rot_dim]) and the down projection ckv [T, ldc] -> heads' outputs in mix_
+    void latent_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& mark, void* q, int ldq, void* ckv, int ldc);
+    // attention over cached keys and values: q / k / v [T, ld] -> heads' outputs in mix_ (gate: null or [T, ldg])
+    void window_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& mark, void* q, void* k, void* v, int ld,
+                      const void* gate, int ldg);
+    void forward_sequential(const HyRows& r, const std::vector<TileList>& tile_lists, const int32_t* d_tokens, const std::function<void(int)>& mark);
+    HyLatentAttn latent_params(const HyLayer& l, const LayerW& w) const;
     void linear_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const std::function<void(int)>& mark);
     bool has_tensor(const std::string& name) const;
     int cache_row_width(const HyLayer& l) const { return (l.type == HY_WINDOW_ATTENTION || l.type == HY_ATTENTION_BESIDE_MEMORY) ? l.kv_heads * (l.maps * l.dim + l.vdim) : l.kv_rank + l.rot_dim; }
@@ -75,6 +90,8 @@ private:
     void* embed_ = nullptr; Mat head_, loop_in_; float *loop_step_ = nullptr, *final_norm_ = nullptr;
     std::vector<void*> caches_;                    // per attention execution: [num_pages * 64][kv_rank + rot_dim] in the activation type
     std::vector<float*> states_; std::vector<void*> tails_;      // per recurrent execution: [slots][heads * dim * vdim] fp32, [slots][(taps - 1) * channels]
+    std::vector<float*> shift_states_;             // per layer execution of a design with a token shift: [slots][width] fp32, the last normed row of the sequence
+    float *xs_ = nullptr, *hn_ = nullptr, *shift_prev_ = nullptr, *ones_ = nullptr; void* cq_ = nullptr; int ld_cq_ = 0, n_streams_ = 1;      // residual streams [T, n, W]; normed rows before the shift; carried rows of the step's sequences
     std::vector<float*> aux_;                      // per matrix-memory execution: [slots][heads * dim] normaliser, then [slots][heads] running maximum
     int MR_ = 0, MS_ = 0, Wld_ = 0;
     // activations

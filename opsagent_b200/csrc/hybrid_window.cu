@@ -158,6 +158,36 @@ __device__ __forceinline__ float win_tanh(float x) {          // 1 - 2 / (e^2x +
     return 1.0f - 2.0f / (e + 1.0f);
 }
 
+// Rotary preparation: per row, the first rot.dims channels of every query head (in place) and key head turn by the row's position, every
+// value head turns over all of its channels (v_cos given); keys and values go to the row's cache slot.  A thread owns a pair of channels.
+template <typename TA>
+__device__ __forceinline__ void rope_head(const TA* src, TA* dst, int n, int dims, int layout, const float* cs, const float* sn, int i) {
+    // i < n / 2 + (n - dims) / 2 ... handled by the caller: i indexes pairs first (dims / 2 of them), then the unrotated rest one by one
+    const int half = dims / 2;
+    if (i < half) {
+        const int a = layout ? i : 2 * i, b = layout ? i + half : 2 * i + 1;
+        const float u = ldf(src + a), v = ldf(src + b);
+        stf(dst + a, u * cs[i] - v * sn[i]); stf(dst + b, v * cs[i] + u * sn[i]);
+    } else { const int c = dims + (i - half); if (src != dst) stf(dst + c, ldf(src + c)); }
+}
+template <typename TA>
+__global__ void __launch_bounds__(128) hy_win_rope_prep_kernel(HyWinAttn a, HyRotary rot, TA* __restrict__ q, int ldq, const TA* __restrict__ k, const TA* __restrict__ v, int ldkv,
+                                                               TA* __restrict__ cache, HyRows r) {
+    HY_PDL();
+    const long long t = blockIdx.x; const int D = a.dim, VD = a.vdim, pos = r.positions[t];
+    const int KW = a.kv_heads * D, CW = KW + a.kv_heads * VD, half = rot.dims / 2, per = half + (D - rot.dims);      // work items per query / key head
+    const float* cs = rot.cos + (long long)pos * half; const float* sn = rot.sin + (long long)pos * half;
+    TA* crow = cache + (long long)r.slots[t] * CW;
+    for (int i = threadIdx.x; i < a.heads * per; i += blockDim.x) { const int hd = i / per; TA* p = q + t * ldq + (long long)hd * D; rope_head(p, p, D, rot.dims, rot.layout, cs, sn, i - hd * per); }
+    if (k) for (int i = threadIdx.x; i < a.kv_heads * per; i += blockDim.x) { const int hd = i / per; rope_head(k + t * ldkv + (long long)hd * D, crow + (long long)hd * D, D, rot.dims, rot.layout, cs, sn, i - hd * per); }
+    if (v) {
+        if (rot.v_cos) {
+            const int vh = VD / 2; const float* vc = rot.v_cos + (long long)pos * vh; const float* vs = rot.v_sin + (long long)pos * vh;
+            for (int i = threadIdx.x; i < a.kv_heads * vh; i += blockDim.x) { const int hd = i / vh; rope_head(v + t * ldkv + (long long)hd * VD, crow + KW + (long long)hd * VD, VD, VD, rot.layout, vc, vs, i - hd * vh); }
+        } else for (int c = threadIdx.x; c < a.kv_heads * VD; c += blockDim.x) crow[KW + c] = v[t * ldkv + c];
+    }
+}
+
 // The visible keys of a query at position p, in the order every kernel walks them: the kept first positions that the window no longer
 // covers, then the window.  n = count; key(i) = i-th visible position.
 struct WinKeys {
@@ -250,6 +280,23 @@ __global__ void __launch_bounds__(128) hy_win_attention_kernel(HyWinAttn a, cons
     }
     float post = 1.f;
     if (NM == 2) post = a.out_scale / sqrtf(block_sum(ss, red) / (float)VD + eps);
+    if (a.out_rot) {                 // the head's output turned back by its own position: channels meet their partners through shared memory
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < WIN_MAXV / 4; ++i) { const int c = threadIdx.x + 128 * i; if (c < VD) part[c] = o[i] * post; }
+        __syncthreads();
+        const int vh = VD / 2; const float* cs = a.out_cos + (long long)pos * vh; const float* sn = a.out_sin + (long long)pos * vh;
+#pragma unroll
+        for (int i = 0; i < WIN_MAXV / 4; ++i) {
+            const int c = threadIdx.x + 128 * i;
+            if (c < VD) {
+                const bool first = a.out_rot == 1 ? !(c & 1) : c < vh; const int pr = a.out_rot == 1 ? c >> 1 : (first ? c : c - vh);
+                const int other = a.out_rot == 1 ? c ^ 1 : (first ? c + vh : c - vh);
+                o[i] = first ? part[c] * cs[pr] + part[other] * sn[pr] : part[c] * cs[pr] - part[other] * sn[pr];       // (u, v) -> (u cos + v sin, v cos - u sin)
+            }
+        }
+        post = 1.f;
+    }
 #pragma unroll
     for (int i = 0; i < WIN_MAXV / 4; ++i) {
         const int c = threadIdx.x + 128 * i;
@@ -460,6 +507,19 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
             post = a.out_scale / sqrtf(ss / (float)VD + eps);
         }
         if (!ok) continue;
+        if (a.out_rot) {               // the head's output turned back by the row's position; both channels of a pair sit in this thread
+            const int vh = VD / 2, pos = r.positions[row]; const float* cs = a.out_cos + (long long)pos * vh; const float* sn = a.out_sin + (long long)pos * vh;
+            if (a.out_rot == 1) {
+#pragma unroll
+                for (int nb = 0; nb < NVB; ++nb) { const int m = nb * 4 + (lane & 3); const float u = y[nb][0] * post, v = y[nb][1] * post; y[nb][0] = u * cs[m] + v * sn[m]; y[nb][1] = v * cs[m] - u * sn[m]; }
+            } else {
+#pragma unroll
+                for (int nb = 0; nb < NVB / 2; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) { const int m = nb * 8 + (lane & 3) * 2 + e; const float u = y[nb][e] * post, v = y[nb + NVB / 2][e] * post; y[nb][e] = u * cs[m] + v * sn[m]; y[nb + NVB / 2][e] = v * cs[m] - u * sn[m]; }
+            }
+            post = 1.f;
+        }
         if (a.gate == 2) post *= sigmoidf_(__bfloat162float(gate[(long long)row * ldg + head]));
         __nv_bfloat16* dst = out + (long long)row * ldo + (long long)head * VD + (lane & 3) * 2;
         const __nv_bfloat16* gp = gate + (long long)row * ldg + (long long)head * VD + (lane & 3) * 2;
@@ -660,6 +720,15 @@ __global__ void __launch_bounds__(256) hy_win_decode_mma_kernel(HyWinAttn a, con
         for (int sh = 1; sh < 16; sh <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sh);
         post = a.out_scale / sqrtf(ss / (float)VD + eps);
     }
+    if (a.out_rot == 1) {              // the head's output turned back by the row's position: channel c meets c ^ 1 in the neighbouring lane
+        const int vh = VD / 2, pos = r.positions[row]; const float* cs = a.out_cos + (long long)pos * vh; const float* sn = a.out_sin + (long long)pos * vh;
+#pragma unroll
+        for (int i = 0; i < NVB / 2; ++i) {
+            const int c = sub + 16 * i; const float mine = y[i] * post, other = __shfl_xor_sync(0xffffffffu, mine, 1);
+            y[i] = (c & 1) ? mine * cs[c >> 1] - other * sn[c >> 1] : mine * cs[c >> 1] + other * sn[c >> 1];
+        }
+        post = 1.f;
+    }
     if (!ok) return;
     if (a.gate == 2) post *= sigmoidf_(__bfloat162float(gate[(long long)row * ldg + head]));
 #pragma unroll
@@ -700,6 +769,11 @@ cudaError_t hy_win_prep(bool f32, const HyWinAttn& a, void* q, int ldq, const vo
                : launch_plain(hy_win_prep_kernel<bf>, dim3(r.T), dim3(128), 0, s, a, (bf*)q, ldq, (const bf*)k, (const bf*)v, ldkv, q_norm_w, k_norm_w, eps, (bf*)cache, r);
 }
 
+cudaError_t hy_win_rope_prep(bool f32, const HyWinAttn& a, const HyRotary& rot, void* q, int ldq, const void* k, const void* v, int ldkv, void* cache, const HyRows& r, cudaStream_t s) {
+    if (a.maps != 1 || a.qk_norm || (rot.dims & 1) || rot.dims > a.dim || (rot.v_cos && (a.vdim & 1))) return cudaErrorInvalidValue;
+    return f32 ? launch_plain(hy_win_rope_prep_kernel<float>, dim3(r.T), dim3(128), 0, s, a, rot, (float*)q, ldq, (const float*)k, (const float*)v, ldkv, (float*)cache, r)
+               : launch_plain(hy_win_rope_prep_kernel<__nv_bfloat16>, dim3(r.T), dim3(128), 0, s, a, rot, (__nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, ldkv, (__nv_bfloat16*)cache, r);
+}
 bool hy_win_supported(const HyWinAttn& a) {
     return a.maps >= 1 && a.maps <= 2 && a.vdim <= 32 * WIN_MAXV && a.dim >= 1 && a.heads % a.kv_heads == 0 &&
            (size_t)(a.maps * a.dim + 4 * a.maps * a.vdim + 8 * a.maps) * 4 <= 200 * 1024;
@@ -725,7 +799,7 @@ cudaError_t hy_win_attention(bool f32, const HyWinAttn& a, const void* q, int ld
 static bool win_modded(const HyWinAttn& a) { return a.softcap > 0.f || a.slope_exp > 0.f; }
 bool hy_win_mma_supported(const HyWinAttn& a) {
     const bool vd_ok = a.vdim == 16 || a.vdim == 32 || a.vdim == 64 || a.vdim == 96 || a.vdim == 128;
-    return hy_win_supported(a) && a.dim % 16 == 0 && a.dim <= 128 && vd_ok && !(win_modded(a) && a.maps != 1);      // score modifiers on the tensor cores: one map
+    return hy_win_supported(a) && a.dim % 16 == 0 && a.dim <= 128 && vd_ok && !(win_modded(a) && a.maps != 1) && a.out_rot != 2;      // score modifiers on the tensor cores: one map; outputs turned back in pairs of neighbours only
 }
 template <int MAPS, int NVB, bool MOD>
 static cudaError_t win_mma_launch(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,

@@ -16,7 +16,7 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 
 // ---- GEMM (gemm_tcgen05.cu): C[M,N] = A[M,K] . B[N,K]^T, bf16 in, fp32 accumulate in TMEM -------
 enum GemmEpilogue : int {
-    EPI_STORE = 0,    // out[M,N] bf16 = act(acc (+ bias[N])), act = identity or relu(.)^2 (GemmParams::store_act)
+    EPI_STORE = 0,    // out[M,N] bf16 = act(acc (+ bias[N])), act = identity, relu(.)^2 or the tanh form of GELU (GemmParams::store_act)
     EPI_RESID = 1,    // out[M,N] bf16 = acc + resid[M,N]      (out may alias resid)
     EPI_SWIGLU = 2,   // out[M,N/2] bf16 = silu(gate)*up, B rows interleaved 16 gate / 16 up
     EPI_LOGITS = 3,   // per-row (max, argmax) partial per N-tile -> argmax_ws; optional fp32 logits store
@@ -26,7 +26,7 @@ struct GemmParams {
     int M, N, K;
     void* out; int ldo;             // bf16 output, leading dimension in elements
     const void* bias;               // bf16 [N] or null        (EPI_STORE)
-    int store_act;                  // EPI_STORE: 0 = store as is, 1 = relu(.)^2 (gate-less experts' activation)
+    int store_act;                  // EPI_STORE: 0 = store as is, 1 = relu(.)^2 (gate-less experts' activation), 2 = gelu_tanh(.) (dense feed-forward)
     const void* resid; int ldr;     // bf16 [M, ldr]           (EPI_RESID)
     float* logits; int ldl;         // optional fp32 [M, ldl]  (EPI_LOGITS)
     float* amax_val; int* amax_idx; // [M, n_tiles]            (EPI_LOGITS)
