@@ -704,7 +704,7 @@ void HybridModel::forward_sequential(const HyRows& r, const std::vector<TileList
         } else if (l.type == HY_WINDOW_ATTENTION) {
             void* src = proj_; int ld = ld_proj_;
             if (l.conv > 0) {
-                cuda_check(hy_conv_silu(f32_, proj_, ld_proj_, w.conv_ch, w.conv_w, nullptr, l.conv, conv_, ld_conv_, tails_[run.state_idx >= 0 ? run.state_idx : 0], r, stream, 0), "conv");
+                cuda_check(hy_conv_silu(f32_, proj_, ld_proj_, w.conv_ch, w.conv_w, nullptr, l.conv, conv_, ld_conv_, run.state_idx >= 0 ? tails_[run.state_idx] : nullptr, r, stream, 0), "conv");
                 if (l.conv > 1) cuda_check(hy_conv_tails(f32_, proj_, ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails");
                 MARK(6); src = conv_; ld = ld_conv_;
             }
