@@ -608,8 +608,8 @@ def main():
     ap.add_argument("--engine-extra", default="{}", dest="engine_extra", help="dev: JSON of engine options merged into the config (A/B runs)")
     ap.add_argument("--tp-deadline", type=float, default=900.0, dest="tp_deadline")
     ap.add_argument("--tp-only", action="store_true", help="dev: only the tensor-parallel block (prints {\"tp\": ...}; NOT a bench line)")
-    ap.add_argument("--arch", default="", choices=["", "ratasun", "zurevik", "rofizen"], help="ratasun: prefill / decode throughput of the hybrid family at layer sizes of a real model beside "
-                    "the Llama-family model of equal width, depth and active feed-forward size; zurevik / rofizen: the same for that design, beside the Ratasun model of equal "
+    ap.add_argument("--arch", default="", choices=["", "ratasun", "zurevik", "rofizen", "gosavik"], help="ratasun: prefill / decode throughput of the hybrid family at layer sizes of a real model beside "
+                    "the Llama-family model of equal width, depth and active feed-forward size; zurevik / rofizen / gosavik: the same for that design, beside the Ratasun model of equal "
                     "width, depth and experts and that Llama-family model (its own JSON line; the default workload is untouched)")
     ap.add_argument("--arch-sizes", default="small,medium", dest="arch_sizes")
     ap.add_argument("--arch-batch", type=int, default=16, dest="arch_batch")

@@ -502,8 +502,13 @@ __global__ void __launch_bounds__(128) hy_mha_prefill_mma_kernel(HyLatentAttn a,
         }
         const float inv = l > 0.f ? up / l : 0.f;
         __nv_bfloat16* dst = mix + (long long)(row0 + qi) * ld_mix + h * VD + (lane & 3) * 2;
+        const __nv_bfloat16* gp = a.gate ? reinterpret_cast<const __nv_bfloat16*>(a.gate) + (long long)(row0 + qi) * a.ldg + h * VD + (lane & 3) * 2 : nullptr;
 #pragma unroll
-        for (int nb = 0; nb < NVB; ++nb) *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16x2(o[nb][half * 2] * inv, o[nb][half * 2 + 1] * inv);
+        for (int nb = 0; nb < NVB; ++nb) {
+            float y0 = o[nb][half * 2] * inv, y1 = o[nb][half * 2 + 1] * inv;
+            if (gp) { const uint32_t gg = *reinterpret_cast<const uint32_t*>(gp + nb * 8); y0 *= sigmoidf_(bf16lo(gg)); y1 *= sigmoidf_(bf16hi(gg)); }
+            *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16x2(y0, y1);
+        }
     }
 }
 // cache rows 0 .. ctx-1 of the listed sequences, contiguous: lat_ctx[seq_base[s] + j] = cache row j of sequence s (seq_base < 0: not listed)

@@ -96,6 +96,8 @@ struct HyLatentAttn {             // sizes of one latent-attention layer
     // optional parts: window > 0: position i sees j with 0 <= i - j < window (0: every j <= i); rot_layout 1: rotary pairs channel i with
     // i + rot_dims / 2 instead of 2i with 2i + 1; sink (device, one fp32 logit per head): joins the softmax denominator only, unscaled
     int window = 0, rot_layout = 0; const float* sink = nullptr;
+    // prefill form only: out[t, c] *= sigmoid(gate[t, c]) over the concatenated heads (bf16, pitch ldg), in the attention kernel's epilogue
+    const void* gate = nullptr; int ldg = 0;
 };
 // From the q projection (q: [T, ldq], head by head [dim | rot_dim]) and the down projection (ckv: [T, ldc] = [kv_rank | rot_dim]):
 // latent = rmsnorm(ckv[:rank]) * norm_w and the rotated shared key go to cache row slots[t] ([rank + rot_dim] per row); the rotated query
@@ -204,7 +206,7 @@ cudaError_t hy_embed_streams(bool f32, const int32_t* ids, const void* table, fl
 // One pass over the rows, each part optional:
 //  (1) y != null: the sublayer that has just run closes, all streams at once from the old ones: x_t <- sum_s upd_mix[s * n + t] x_s + upd_out[t] y   (y [T, W] fp32)
 //  (2) w != null: the next sublayer's input u = sum_s in[s] x_s, v = u / sqrt(mean(u^2) + eps) * w.  rows != null: row t of the output reads row
-//      rows[t] of xs (the rows whose logits are wanted); then (1) is not allowed.
+//      rows[t] of xs and of y (the rows whose logits are wanted); then (1) only enters u, the streams themselves stay, and no token shift follows.
 //      shift_state == null: v goes to h[t] (activation type, pitch ldh).
 //      shift_state != null (token shift follows): v goes to hn[t] (fp32 [T, W]); the CTA of a sequence's last row also moves the sequence's carried
 //      row shift_state[slot] to prev[seq] and stores v in its place.  hy_token_shift then makes h[t] = v_t + (v_(t-1) - v_t) * mu, with v_(t-1) from

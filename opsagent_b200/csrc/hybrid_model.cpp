@@ -637,7 +637,8 @@ void HybridModel::window_mixer(const HyRun& run, const HyLayer& l, const LayerW&
     MARK(24);
 }
 
-void HybridModel::latent_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& MARK, void* q, int ldq, void* ckv, int ldc) {
+void HybridModel::latent_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& MARK, void* q, int ldq, void* ckv, int ldc,
+                               const void* gate, int ldg) {
     auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
     const int T = r.T;
     const HyLatentAttn a = latent_params(l, w);
@@ -661,11 +662,13 @@ void HybridModel::latent_mixer(const HyRun& run, const HyLayer& l, const LayerW&
         else cuda_check(hy_gemm(f32_, HY_STORE, lat_, l.heads * l.kv_rank, w.uv, l.kv_rank, mix_, ld_mix_, T, l.vdim, l.kv_rank, nullptr, 1.f, l.heads, l.kv_rank,
                                 (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection");
         MARK(3);
+        if (gate) { cuda_check(hy_sigmoid_gate(f32_, mix_, ld_mix_, gate, ldg, l.heads * l.vdim, T, stream), "output gate"); MARK(9); }
     }
     if (tl.n_ptiles > 0) {      // prefill form for the sequences that bring many rows (after the absorbed path, whose up-projection wrote every row of mix_)
         cuda_check(hy_gather_ctx(caches_[run.cache_idx], E, r, d_meta_ + tl.o_base, tl.max_ctx, lat_ctx_, stream), "context gather");
         gemm(HY_STORE, lat_ctx_, E, w.kv_up, kv_ctx_, ld_kv_, tl.ctx_rows, nullptr, 1.f); MARK(20);
-        cuda_check(hy_mha_prefill(a, q, ldq, q_abs_, kv_ctx_, ld_kv_, lat_ctx_, mix_, ld_mix_, r, d_meta_ + tl.o_pseq, d_meta_ + tl.o_phead,
+        HyLatentAttn ag = a; ag.gate = gate; ag.ldg = ldg;          // the gate rides in the attention kernel's epilogue
+        cuda_check(hy_mha_prefill(ag, q, ldq, q_abs_, kv_ctx_, ld_kv_, lat_ctx_, mix_, ld_mix_, r, d_meta_ + tl.o_pseq, d_meta_ + tl.o_phead,
                                   d_meta_ + tl.o_prow0, d_meta_ + tl.o_base, tl.n_ptiles, stream), "attention (prefill form)"); MARK(21);
     }
 }
@@ -699,8 +702,7 @@ void HybridModel::forward_sequential(const HyRows& r, const std::vector<TileList
                 gemm(HY_STORE, cq_, ld_cq_, w.uq, p2_, ld_p2_, T, nullptr, 1.f); MARK(10);
                 q = p2_; ldq = ld_p2_;
             }
-            latent_mixer(run, l, w, r, tile_lists[run.layer], MARK, q, ldq, at(proj_, w.off_b), ld_proj_);
-            if (l.gate == HY_GATE_CHANNEL) { cuda_check(hy_sigmoid_gate(f32_, mix_, ld_mix_, at(proj_, w.off_d), ld_proj_, l.heads * l.vdim, T, stream), "output gate"); MARK(9); }
+            latent_mixer(run, l, w, r, tile_lists[run.layer], MARK, q, ldq, at(proj_, w.off_b), ld_proj_, l.gate == HY_GATE_CHANNEL ? at(proj_, w.off_d) : nullptr, ld_proj_);
         } else if (l.type == HY_WINDOW_ATTENTION) {
             void* src = proj_; int ld = ld_proj_;
             if (l.conv > 0) {
@@ -726,7 +728,7 @@ void HybridModel::forward_sequential(const HyRows& r, const std::vector<TileList
             for (int t = 0; t < T; ++t) for (int sidx = 0; sidx < n; ++sidx) for (int c = 0; c < W; ++c) (*capture_layers)[n0 + (size_t)t * W + c] += tmp[((size_t)t * n + sidx) * W + c];
         }
     }
-    if (pending) open(nullptr, nullptr, nullptr, "streams (last sublayer)");
+    pending_ = pending; pend_mix_ = pend_mix; pend_out_ = pend_out;      // the final norm folds the last y_ into the rows it reads; the streams themselves are not needed again
 }
 
 void HybridModel::forward(const StepInput& in, float* logits_out) {
@@ -918,8 +920,8 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     }
     if (NS > 0) {
         if (hc_.sequential) {      // x = the sum of the streams, of the wanted rows only
-            const HyStreams fin{n_streams_, nullptr, nullptr, ones_};
-            cuda_check(hy_stream_norm(f32_, fin, xs_, nullptr, d_meta_ + o_samp, final_norm_, hc_.eps, hs_, Wld_, nullptr, nullptr, nullptr, r, NS, W, stream), "final norm");
+            const HyStreams fin{n_streams_, pend_mix_, pend_out_, ones_};
+            cuda_check(hy_stream_norm(f32_, fin, xs_, pending_ ? y_ : nullptr, d_meta_ + o_samp, final_norm_, hc_.eps, hs_, Wld_, nullptr, nullptr, nullptr, r, NS, W, stream), "final norm");
         } else if (hc_.norm == HY_RMS_NORM) cuda_check(hy_rmsnorm_pair(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, nullptr, nullptr, Wld_, NS, W, hc_.eps, stream), "final norm");
         else cuda_check(hy_layernorm(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, Wld_, NS, W, hc_.eps, stream), "final norm");
         if (!logits_out && NS > opt.max_batch) throw std::runtime_error("forward: more sampled rows than sequences need a caller's logits buffer");

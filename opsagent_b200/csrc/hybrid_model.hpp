@@ -73,7 +73,8 @@ private:
     void moe(const LayerW& w, const HyLayer& l, const void* h, const HyRows& r, const std::function<void(int)>& mark, const int32_t* tokens = nullptr, float beta = 1.f);
     int rope_table(float base, int dims, const HyRotScaling* sc = nullptr);
     // latent attention of one layer execution: q [T, ldq] (head by head [dim | rot_dim]) and the down projection ckv [T, ldc] -> heads' outputs in mix_
-    void latent_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& mark, void* q, int ldq, void* ckv, int ldc);
+    void latent_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& mark, void* q, int ldq, void* ckv, int ldc,
+                      const void* gate = nullptr, int ldg = 0);          // gate: sigmoid output gate per channel of the concatenated heads
     // attention over cached keys and values: q / k / v [T, ld] -> heads' outputs in mix_ (gate: null or [T, ldg])
     void window_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& mark, void* q, void* k, void* v, int ld,
                       const void* gate, int ldg);
@@ -91,6 +92,7 @@ private:
     std::vector<void*> caches_;                    // per attention execution: [num_pages * 64][kv_rank + rot_dim] in the activation type
     std::vector<float*> states_; std::vector<void*> tails_;      // per recurrent execution: [slots][heads * dim * vdim] fp32, [slots][(taps - 1) * channels]
     std::vector<float*> shift_states_;             // per layer execution of a design with a token shift: [slots][width] fp32, the last normed row of the sequence
+    const float *pend_mix_ = nullptr, *pend_out_ = nullptr; bool pending_ = false;      // the last sublayer's y_ is folded into the streams by whoever reads them next
     float *xs_ = nullptr, *hn_ = nullptr, *shift_prev_ = nullptr, *ones_ = nullptr; void* cq_ = nullptr; int ld_cq_ = 0, n_streams_ = 1;      // residual streams [T, n, W]; normed rows before the shift; carried rows of the step's sequences
     std::vector<float*> aux_;                      // per matrix-memory execution: [slots][heads * dim] normaliser, then [slots][heads] running maximum
     int MR_ = 0, MS_ = 0, Wld_ = 0;

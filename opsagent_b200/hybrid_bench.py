@@ -1,6 +1,8 @@
-"""Throughput of the hybrid family beside the closest existing models (`bench.py --arch ratasun | zurevik | rofizen`): Ratasun beside the
+"""Throughput of the hybrid family beside the closest existing models (`bench.py --arch ratasun | zurevik | rofizen | gosavik`): Ratasun beside the
 Llama-family model of equal width, depth and active feed-forward size; Zurevik and Rofizen beside the Ratasun model of equal width, depth and
-experts (the closest design: routed experts in every layer; recurrent mixers with an fp32 state like Rofizen's) and beside that Llama-family model.  Random weights (seeded on load), synthetic token ids; prefill = real chunked prefill of batch x (ctx-1) tokens,
+experts (the closest design: routed experts in every layer; recurrent mixers with an fp32 state like Rofizen's) and beside that Llama-family model;
+Gosavik (dense feed-forward, attention mixers only) beside the Llama-family model of equal width, depth and feed-forward size — the closest model as a whole —
+and beside Ratasun, whose latent attention is the closest kernel to its own.  Random weights (seeded on load), synthetic token ids; prefill = real chunked prefill of batch x (ctx-1) tokens,
 decode = steps of the whole batch, both timed with CUDA events inside the engine (oa_bench_decode).  With --breakdown the per-kernel-class
 device times come from the engine's in-situ event timing (OA_PROFILE_ALL), one pass for prefill and one for decode."""
 from __future__ import annotations
@@ -68,6 +70,24 @@ def rofizen_sizes(name: str) -> dict:
             "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in order]}
 
 
+def gosavik_sizes(name: str) -> dict:
+    """Gosavik at the width and depth (6 layer executions: latent attention, then [attention, latent attention] twice with the same weights, then
+    attention) of sizes(name), with a dense feed-forward of the Llama case's size, four residual streams, windows of 512 and YaRN-scaled rotary."""
+    if name == "small":
+        lat = {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "q_rank": 384, "scale": 96 ** -0.5}
+        att = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64, "conv": 4, "scale": 64 ** -0.5, "rot": {"base": 500000.0, "dims": 64}}
+        width, ff = 1024, 2048
+    else:
+        lat = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 768, "scale": 192 ** -0.5}
+        att = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5, "rot": {"base": 500000.0, "dims": 128}}
+        width, ff = 2048, 4096
+    lat.update(mask={"size": 512}, rot={"base": 10000.0, "dims": lat["rot_dim"], "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}})
+    mlp = {"kind": "dense", "ff": ff}
+    order = [("latent_attention", lat), ("attention", att), ("latent_attention", lat), ("attention", att)]
+    return {"architecture": "Gosavik", "width": width, "vocab": 32000, "norm": {"eps": 1e-5}, "streams": 4, "loop": {"start": 1, "stop": 3, "times": 2},
+            "layers": [{"type": t, "mixer": m, "mlp": mlp} for t, m in order]}
+
+
 def one(engine_cfg: dict, batch: int, ctx: int, steps: int, warmup: int, breakdown: bool) -> dict:
     from .engine import Engine
     out = {}
@@ -93,7 +113,7 @@ def one(engine_cfg: dict, batch: int, ctx: int, steps: int, warmup: int, breakdo
 
 
 def run(args) -> None:
-    zu = args.arch in ("zurevik", "rofizen")
+    zu = args.arch in ("zurevik", "rofizen", "gosavik")
     res = {"metric": args.arch + "_vs_ratasun_and_llama_throughput" if zu else "hybrid_vs_llama_throughput", "unit": "tokens/s", "data": "synthetic", "dtype": "bf16", "cases": []}
     for name in args.arch_sizes.split(","):
         sz = sizes(name)
@@ -108,7 +128,7 @@ def run(args) -> None:
                 return one(dict(common, model_dir=d, **json.loads(args.engine_extra)), batch, ctx, args.steps, args.warmup, args.breakdown)
         case = {"size": name, "batch": batch, "ctx": ctx, "layer_runs": sz["runs"]}
         if zu:
-            case[args.arch] = folder_model(zurevik_sizes(name) if args.arch == "zurevik" else rofizen_sizes(name))
+            case[args.arch] = folder_model({"zurevik": zurevik_sizes, "rofizen": rofizen_sizes, "gosavik": gosavik_sizes}[args.arch](name))
         case["ratasun"] = hy = folder_model(sz["hybrid"])
         case["llama_equal_size"] = ll = one(dict(common, **sz["llama"]), batch, ctx, args.steps, args.warmup, args.breakdown)
         new = case[args.arch] if zu else hy
