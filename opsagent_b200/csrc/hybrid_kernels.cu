@@ -65,6 +65,44 @@ __global__ void __launch_bounds__(256) hy_gemm_kernel(const TA* __restrict__ A, 
     }
 }
 
+// The same product for a handful of rows (decoding steps), bf16 operands with K in aligned groups of 8: one warp per output column keeps
+// its row of B in registers (K <= 1024: four 16-byte pieces per lane) and walks the M rows of A; a lane sums its pieces in order, then the
+// warp joins by a butterfly, so a row's result does not depend on the other rows.  The tile kernel above leaves most of a 64-row tile empty
+// at these sizes and runs K / 16 barrier-separated slices on a few CTAs.
+template <int MODE>
+__global__ void __launch_bounds__(256) hy_gemm_fewrows_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ B, int ldb, void* Cv, int ldc, int M, int N,
+                                                              int K, const float* __restrict__ bias, float alpha, long long sA, long long sB, long long sC, int act) {
+    HY_PDL();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    A += (long long)blockIdx.y * sA; B += (long long)blockIdx.y * sB;
+    uint4 b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const int k = (lane + 32 * i) * 8; b[i] = k < K ? *reinterpret_cast<const uint4*>(B + (long long)n * ldb + k) : make_uint4(0, 0, 0, 0); }
+    for (int m = 0; m < M; ++m) {
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = (lane + 32 * i) * 8;
+            if (k < K) {
+                const uint4 a = *reinterpret_cast<const uint4*>(A + (long long)m * lda + k);
+                acc = fmaf(bf16lo(a.x), bf16lo(b[i].x), acc); acc = fmaf(bf16hi(a.x), bf16hi(b[i].x), acc); acc = fmaf(bf16lo(a.y), bf16lo(b[i].y), acc); acc = fmaf(bf16hi(a.y), bf16hi(b[i].y), acc);
+                acc = fmaf(bf16lo(a.z), bf16lo(b[i].z), acc); acc = fmaf(bf16hi(a.z), bf16hi(b[i].z), acc); acc = fmaf(bf16lo(a.w), bf16lo(b[i].w), acc); acc = fmaf(bf16hi(a.w), bf16hi(b[i].w), acc);
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            float v = acc * alpha + (bias ? bias[n] : 0.f);
+            if (act == 1) { v = fmaxf(v, 0.f); v *= v; }
+            else if (act == 2) v = gelu_tanhf_(v);
+            const long long at = (long long)blockIdx.y * sC + (long long)m * ldc + n;
+            if (MODE == HY_STORE) reinterpret_cast<__nv_bfloat16*>(Cv)[at] = __float2bfloat16_rn(v);
+            else if (MODE == HY_STORE_F32) reinterpret_cast<float*>(Cv)[at] = v;
+            else reinterpret_cast<float*>(Cv)[at] += v;
+        }
+    }
+}
+
 template <typename TA>
 __global__ void hy_embed_kernel(const int32_t* ids, const TA* table, float* x, float* x0, int T, int W, int vocab, float scale, TA* h, int ldh) {
     HY_PDL();
@@ -1161,6 +1199,15 @@ static cudaError_t gemm_t(int mode, const void* A, int lda, const void* B, int l
 cudaError_t hy_gemm(bool f32, int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias, float alpha, int batch,
                     long long sA, long long sB, long long sC, cudaStream_t s, int act) {
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return cudaSuccess;
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (!f32 && M <= HY_GEMM_FEW_ROWS && K % 8 == 0 && K <= 1024 && lda % 8 == 0 && ldb % 8 == 0 && sA % 8 == 0 && sB % 8 == 0 && al16(A) && al16(B)) {
+        const dim3 grid((N + 7) / 8, batch);
+        switch (mode) {
+            case HY_STORE: return launch_plain(hy_gemm_fewrows_kernel<HY_STORE>, grid, dim3(256), 0, s, (const bf*)A, lda, (const bf*)B, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC, act);
+            case HY_STORE_F32: return launch_plain(hy_gemm_fewrows_kernel<HY_STORE_F32>, grid, dim3(256), 0, s, (const bf*)A, lda, (const bf*)B, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC, act);
+            default: return launch_plain(hy_gemm_fewrows_kernel<HY_ACC_F32>, grid, dim3(256), 0, s, (const bf*)A, lda, (const bf*)B, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC, act);
+        }
+    }
     return f32 ? gemm_t<float>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s, act)
                : gemm_t<bf>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s, act);
 }

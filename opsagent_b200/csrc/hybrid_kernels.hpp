@@ -30,6 +30,8 @@ enum HyGemmMode : int { HY_STORE = 0, HY_STORE_F32 = 1, HY_ACC_F32 = 2 };
 // C[z][M,N] (op)= alpha * A[z][M,K] . B[z][N,K]^T (+ bias[N]), z < batch with element strides sA/sB/sC.  Plain tiled FMA GEMM in fp32
 // accumulation for any sizes: the fp32 mode's matrix product, and the bf16 mode's fallback where a shape does not fit the tensor-core tiles.
 // act = 1: the stored value is relu(.)^2, act = 2: the tanh form of GELU (HY_STORE / HY_STORE_F32)
+// bf16 steps of at most HY_GEMM_FEW_ROWS rows with K <= 1024 in aligned groups of 8 take a one-warp-per-output-column kernel instead of the tile kernel
+constexpr int HY_GEMM_FEW_ROWS = 32;
 cudaError_t hy_gemm(bool f32, int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias,
                     float alpha, int batch, long long sA, long long sB, long long sC, cudaStream_t s, int act = 0);
 
@@ -67,6 +69,13 @@ struct HyWinAttn { int heads, kv_heads, dim, vdim, maps, window, keep_first, qk_
 // with v_cos / v_sin ([position, vdim / 2]) every value head turns over all of its channels in the same layout; keys and values go to cache row slots[t].
 struct HyRotary { int dims, layout; const float* cos; const float* sin; const float* v_cos; const float* v_sin; };
 cudaError_t hy_win_rope_prep(bool f32, const HyWinAttn& a, const HyRotary& rot, void* q, int ldq, const void* k, const void* v, int ldkv, void* cache, const HyRows& r, cudaStream_t s);
+// The same preparation fused with the short convolutions in front of it (bf16; taps 2 .. 4; interleaved pairs; dim, vdim and the segment
+// offsets multiples of 8): `in` [T, ld_in] is the fused projection with the segments q / k / v at columns off_q / off_k / off_v, w [C, taps]
+// the taps of all of its C columns, tails the sequences' carried inputs as hy_conv_silu reads them (hy_conv_tails stores the new ones
+// afterwards).  The fp32 convolution goes straight into the rotation; queries land in q_out [T, ldq] (head by head), keys and values in the cache.
+bool hy_conv_rope_cache_supported(const HyWinAttn& a, const HyRotary& rot, int taps);
+cudaError_t hy_conv_rope_cache(const HyWinAttn& a, const HyRotary& rot, const void* in, int ld_in, int C, int off_q, int off_k, int off_v, const float* w, int taps, void* q_out, int ldq,
+                               void* cache, const void* tails, const HyRows& r, cudaStream_t s);
 bool hy_win_supported(const HyWinAttn& a);
 // q [T, ldq] (head by head, map by map): RMS-normed in place with q_norm_w when qk_norm; k / v [T, ldkv] (null: this layer reads a cache
 // another layer fills): keys normed alike with k_norm_w, both stored at cache row slots[t].  qk_norm = 2: one norm over the row's whole q (k) projection,

@@ -621,15 +621,16 @@ HyLatentAttn HybridModel::latent_params(const HyLayer& l, const LayerW& w) const
 }
 
 void HybridModel::window_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& MARK, void* q, void* k, void* v, int ld,
-                               const void* gate, int ldg) {
+                               const void* gate, int ldg, bool prepared) {
     HyWinAttn a{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, w.lambda, 1.f - l.diff};
     if (l.v_rot) { a.out_rot = l.rot_layout == HY_ROT_HALVES ? 2 : 1; a.out_cos = ropes_[w.rope_v].cos; a.out_sin = ropes_[w.rope_v].sin; }
-    if (l.rot_dims > 0 || l.v_rot) {
+    if (prepared) {}
+    else if (l.rot_dims > 0 || l.v_rot) {
         const HyRotary rot{l.rot_dims, l.rot_layout, l.rot_dims > 0 ? ropes_[w.rope].cos : nullptr, l.rot_dims > 0 ? ropes_[w.rope].sin : nullptr,
                            l.v_rot ? ropes_[w.rope_v].cos : nullptr, l.v_rot ? ropes_[w.rope_v].sin : nullptr};
         cuda_check(hy_win_rope_prep(f32_, a, rot, q, ld, k, v, ld, caches_[run.cache_idx], r, stream), "rotary + cache write");
     } else cuda_check(hy_win_prep(f32_, a, q, ld, k, v, ld, w.q_norm, w.k_norm, hc_.eps, caches_[run.cache_idx], r, stream), "query / key norm + cache write");
-    MARK(23);
+    if (!prepared) MARK(23);
     if (tl.mma) {
         cuda_check(hy_win_attention_mma(a, q, ld, caches_[run.cache_idx], w.sink, gate, ldg, mix_, ld_mix_, hc_.eps, r, d_meta_ + tl.o_wseq, d_meta_ + tl.o_wq0, tl.n_w, stream), "windowed attention (mma)");
         cuda_check(hy_win_decode_mma(a, q, ld, caches_[run.cache_idx], w.sink, gate, ldg, mix_, ld_mix_, hc_.eps, r, d_meta_ + tl.o_dseq, d_meta_ + tl.o_dq0, tl.n_d, stream), "windowed attention (mma, decoding rows)");
@@ -705,12 +706,23 @@ void HybridModel::forward_sequential(const HyRows& r, const std::vector<TileList
             latent_mixer(run, l, w, r, tile_lists[run.layer], MARK, q, ldq, at(proj_, w.off_b), ld_proj_, l.gate == HY_GATE_CHANNEL ? at(proj_, w.off_d) : nullptr, ld_proj_);
         } else if (l.type == HY_WINDOW_ATTENTION) {
             void* src = proj_; int ld = ld_proj_;
+            const HyWinAttn wa = win_params(l, 0.f);
+            const HyRotary rot{l.rot_dims, l.rot_layout, l.rot_dims > 0 ? ropes_[w.rope].cos : nullptr, l.rot_dims > 0 ? ropes_[w.rope].sin : nullptr,
+                               l.v_rot ? ropes_[w.rope_v].cos : nullptr, l.v_rot ? ropes_[w.rope_v].sin : nullptr};
+            if (!f32_ && l.conv > 1 && run.cache_owner && hy_conv_rope_cache_supported(wa, rot, l.conv)) {
+                // convolution, rotation and cache write in one kernel; the fp32 convolution is rounded once, after the rotation
+                cuda_check(hy_conv_rope_cache(wa, rot, proj_, ld_proj_, w.conv_ch, w.off_a, w.off_b, w.off_c, w.conv_w, l.conv, at(conv_, w.off_a), ld_conv_, caches_[run.cache_idx],
+                                              tails_[run.state_idx], r, stream), "conv + rotary + cache write");
+                cuda_check(hy_conv_tails(f32_, proj_, ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails"); MARK(6);
+                window_mixer(run, l, w, r, tile_lists[run.layer], MARK, at(conv_, w.off_a), nullptr, nullptr, ld_conv_, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, true);
+            } else {
             if (l.conv > 0) {
                 cuda_check(hy_conv_silu(f32_, proj_, ld_proj_, w.conv_ch, w.conv_w, nullptr, l.conv, conv_, ld_conv_, run.state_idx >= 0 ? tails_[run.state_idx] : nullptr, r, stream, 0), "conv");
                 if (l.conv > 1) cuda_check(hy_conv_tails(f32_, proj_, ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails");
                 MARK(6); src = conv_; ld = ld_conv_;
             }
             window_mixer(run, l, w, r, tile_lists[run.layer], MARK, at(src, w.off_a), at(src, w.off_b), at(src, w.off_c), ld, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_);
+            }
         } else throw std::runtime_error("forward: this design has no such mixer");
         gemm(HY_STORE_F32, mix_, ld_mix_, w.o, y_, W, T, w.o_bias, 1.f); MARK(11);
         pending = true; pend_mix = hyper ? w.hc_mix[0] : ones_; pend_out = hyper ? w.hc_out[0] : ones_;

@@ -77,7 +77,7 @@ private:
                       const void* gate = nullptr, int ldg = 0);          // gate: sigmoid output gate per channel of the concatenated heads
     // attention over cached keys and values: q / k / v [T, ld] -> heads' outputs in mix_ (gate: null or [T, ldg])
     void window_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const TileList& tl, const std::function<void(int)>& mark, void* q, void* k, void* v, int ld,
-                      const void* gate, int ldg);
+                      const void* gate, int ldg, bool prepared = false);      // prepared: queries are rotated and the cache row is written already
     void forward_sequential(const HyRows& r, const std::vector<TileList>& tile_lists, const int32_t* d_tokens, const std::function<void(int)>& mark);
     HyLatentAttn latent_params(const HyLayer& l, const LayerW& w) const;
     void linear_mixer(const HyRun& run, const HyLayer& l, const LayerW& w, const HyRows& r, const std::function<void(int)>& mark);

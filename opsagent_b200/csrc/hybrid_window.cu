@@ -188,6 +188,79 @@ __global__ void __launch_bounds__(128) hy_win_rope_prep_kernel(HyWinAttn a, HyRo
     }
 }
 
+// Convolution, rotary and cache write in one pass (bf16; interleaved pairs; head sizes and segment offsets in aligned groups of 8 channels): a
+// thread owns 8 channels of ROWS consecutive rows of the fused projection [q | k | v], keeps its taps' weights and the last inputs in
+// registers (every input row is read once; the window is rebuilt from earlier rows, the carried tail or zeros wherever a sequence starts
+// inside the block), and hands the fp32 convolution straight to the rotation: the 4 pairs of a thread's channels turn by the row's position
+// (queries and keys on their first rot.dims channels, values on all), queries go to q_out, keys and values to the row's cache slot.
+// ROWS = 16 for prefill-sized steps, 1 otherwise; a row's arithmetic is the same in both.
+template <int TAPS, int ROWS>
+__global__ void __launch_bounds__(128) hy_conv_rope_cache_kernel(HyWinAttn a, HyRotary rot, const __nv_bfloat16* __restrict__ in, int ld_in, int C, int off_q, int off_k, int off_v,
+                                                                 const float* __restrict__ w, __nv_bfloat16* __restrict__ q_out, int ldq, __nv_bfloat16* __restrict__ cache,
+                                                                 const __nv_bfloat16* __restrict__ tails, HyRows r) {
+    HY_PDL();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8, t0 = blockIdx.y * ROWS;
+    const int D = a.dim, VD = a.vdim, KW = a.kv_heads * D, CW = KW + a.kv_heads * VD;
+    int seg, local;                                      // 0: query, 1: key, 2: value; channel within the segment
+    if (c >= off_q && c < off_q + a.heads * D) { seg = 0; local = c - off_q; }
+    else if (c >= off_k && c < off_k + KW) { seg = 1; local = c - off_k; }
+    else if (c >= off_v && c < off_v + a.kv_heads * VD) { seg = 2; local = c - off_v; }
+    else return;
+    const int d0 = seg == 2 ? local % VD : local % D;    // first of the thread's channels within its head
+    const int n_rot = seg == 2 ? (rot.v_cos ? VD : 0) : rot.dims, half = n_rot / 2;
+    const float* ct = seg == 2 ? rot.v_cos : rot.cos; const float* st = seg == 2 ? rot.v_sin : rot.sin;
+    float wr[TAPS][8], win[TAPS][8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wr[j][e] = w[(c + e) * TAPS + j];
+    auto unpack = [](const uint4& u, float* f) {
+        const uint32_t x[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { f[2 * i] = bf16lo(x[i]); f[2 * i + 1] = bf16hi(x[i]); }
+    };
+    for (int tt = 0; tt < ROWS && t0 + tt < r.T; ++tt) {
+        const int t = t0 + tt, seq = r.row_seq[t], row0 = r.seq_row0[seq], i = t - row0;
+        if (tt == 0 || i == 0) {
+            const int pos0 = r.seq_pos0[seq];
+            const __nv_bfloat16* tail = tails + (long long)r.seq_state[seq] * (TAPS - 1) * C;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) {
+                const int src = i - (TAPS - 1) + j;
+                uint4 u = make_uint4(0u, 0u, 0u, 0u);
+                if (src >= 0) u = *reinterpret_cast<const uint4*>(in + (long long)(row0 + src) * ld_in + c);
+                else if (pos0 > 0) u = *reinterpret_cast<const uint4*>(tail + (long long)(TAPS - 1 + src) * C + c);
+                unpack(u, win[j]);
+            }
+        }
+        unpack(*reinterpret_cast<const uint4*>(in + (long long)t * ld_in + c), win[TAPS - 1]);
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) acc = fmaf(wr[j][e], win[j][e], acc);
+            y[e] = acc;
+        }
+        const long long pos = r.positions[t];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int d = d0 + 2 * p;
+            if (d < n_rot) {
+                const float cs = ct[pos * half + (d >> 1)], sn = st[pos * half + (d >> 1)], u = y[2 * p], v = y[2 * p + 1];
+                y[2 * p] = u * cs - v * sn; y[2 * p + 1] = v * cs + u * sn;
+            }
+        }
+        const uint4 o = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
+        __nv_bfloat16* dst = seg == 0 ? q_out + (long long)t * ldq + local : cache + (long long)r.slots[t] * CW + (seg == 1 ? local : KW + local);
+        *reinterpret_cast<uint4*>(dst) = o;
+#pragma unroll
+        for (int j = 0; j < TAPS - 1; ++j)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) win[j][e] = win[j + 1][e];
+    }
+}
+
 // The visible keys of a query at position p, in the order every kernel walks them: the kept first positions that the window no longer
 // covers, then the window.  n = count; key(i) = i-th visible position.
 struct WinKeys {
@@ -773,6 +846,29 @@ cudaError_t hy_win_rope_prep(bool f32, const HyWinAttn& a, const HyRotary& rot, 
     if (a.maps != 1 || a.qk_norm || (rot.dims & 1) || rot.dims > a.dim || (rot.v_cos && (a.vdim & 1))) return cudaErrorInvalidValue;
     return f32 ? launch_plain(hy_win_rope_prep_kernel<float>, dim3(r.T), dim3(128), 0, s, a, rot, (float*)q, ldq, (const float*)k, (const float*)v, ldkv, (float*)cache, r)
                : launch_plain(hy_win_rope_prep_kernel<__nv_bfloat16>, dim3(r.T), dim3(128), 0, s, a, rot, (__nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, ldkv, (__nv_bfloat16*)cache, r);
+}
+bool hy_conv_rope_cache_supported(const HyWinAttn& a, const HyRotary& rot, int taps) {
+    return a.maps == 1 && !a.qk_norm && taps >= 2 && taps <= 4 && a.dim % 8 == 0 && a.vdim % 8 == 0 && rot.layout == 0 && rot.dims % 2 == 0 && rot.dims <= a.dim;
+}
+template <int TAPS>
+static cudaError_t conv_rope_launch(const HyWinAttn& a, const HyRotary& rot, const void* in, int ld_in, int C, int off_q, int off_k, int off_v, const float* w, void* q_out, int ldq, void* cache,
+                                    const void* tails, const HyRows& r, cudaStream_t s) {
+    using bf = __nv_bfloat16;
+    if (r.T >= 512) return launch_plain(hy_conv_rope_cache_kernel<TAPS, 16>, dim3((C / 8 + 127) / 128, (r.T + 15) / 16), dim3(128), 0, s, a, rot, (const bf*)in, ld_in, C, off_q, off_k, off_v, w,
+                                        (bf*)q_out, ldq, (bf*)cache, (const bf*)tails, r);
+    return launch_plain(hy_conv_rope_cache_kernel<TAPS, 1>, dim3((C / 8 + 127) / 128, r.T), dim3(128), 0, s, a, rot, (const bf*)in, ld_in, C, off_q, off_k, off_v, w, (bf*)q_out, ldq,
+                        (bf*)cache, (const bf*)tails, r);
+}
+cudaError_t hy_conv_rope_cache(const HyWinAttn& a, const HyRotary& rot, const void* in, int ld_in, int C, int off_q, int off_k, int off_v, const float* w, int taps, void* q_out, int ldq,
+                               void* cache, const void* tails, const HyRows& r, cudaStream_t s) {
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (!hy_conv_rope_cache_supported(a, rot, taps) || C % 8 || ld_in % 8 || ldq % 8 || off_q % 8 || off_k % 8 || off_v % 8 || !al16(in) || !al16(q_out) || !al16(cache) || !al16(tails))
+        return cudaErrorInvalidValue;
+    switch (taps) {
+        case 2: return conv_rope_launch<2>(a, rot, in, ld_in, C, off_q, off_k, off_v, w, q_out, ldq, cache, tails, r, s);
+        case 3: return conv_rope_launch<3>(a, rot, in, ld_in, C, off_q, off_k, off_v, w, q_out, ldq, cache, tails, r, s);
+        default: return conv_rope_launch<4>(a, rot, in, ld_in, C, off_q, off_k, off_v, w, q_out, ldq, cache, tails, r, s);
+    }
 }
 bool hy_win_supported(const HyWinAttn& a) {
     return a.maps >= 1 && a.maps <= 2 && a.vdim <= 32 * WIN_MAXV && a.dim >= 1 && a.heads % a.kv_heads == 0 &&
