@@ -1,10 +1,13 @@
-// hybrid_kernels.hpp — launch API of the kernels behind the hybrid decoder family (hybrid_kernels.cu, hybrid_window.cu, hybrid_linear.cu): layer norm and RMS
+// hybrid_kernels.hpp — launch API of the kernels behind the hybrid decoder family (hybrid_kernels.cu, hybrid_window.cu, hybrid_linear.cu, hybrid_streams.cu): layer norm and RMS
 // norm, latent attention over a paged latent cache, windowed attention over paged keys and values (sliding window, kept first tokens,
 // differential maps, sink, output gates, soft cap and distance slope on the scores, a norm over the whole projection, a query temperature),
 // causal short convolutions with carried tails, the linear recurrences (gated delta rule with per-channel decay, Mamba-2, gated linear
 // attention, retention, the xLSTM matrix memory with its normaliser and running maximum) and their operand kernels (hybrid_linear.cu), gated
 // group norms, the norm after the sum of post-norm designs, the routers (group-limited sigmoid; softmax over the chosen logits; a table of
-// token ids) and the routed experts (SwiGLU; squared ReLU).  Each mechanism takes its sizes and constants as arguments.
+// token ids) and the routed experts (SwiGLU; squared ReLU); several residual streams joined by learned coefficients with the RMS norm that
+// opens a sublayer, the token shift, rotary preparation of cached keys and values (also fused with short convolutions), rotated values and
+// the counter-rotation of the heads' outputs, window / sink / gate on latent attention (hybrid_streams.cu, hybrid_window.cu, hybrid_kernels.cu).
+// Each mechanism takes its sizes and constants as arguments.
 //
 // `f32` selects the activation / matrix element type: false = bf16 storage with fp32 accumulation, true = everything in fp32.  What must be
 // fp32 in both modes (residual stream, norms, softmax, router, recurrent state, decays, gates of a recurrence) always is.

@@ -804,9 +804,9 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             tl.any_small = true;
             if (!tl.mma) continue;
             const int ctx = seq_pos0_[sq] + 1, vis0 = l.window > 0 ? std::max(0, ctx - l.window) / 32 * 32 : 0;       // first visible cache row of a decoding row, on a tile border
-            // a decoding row with a long context: its cache rows in 2..16 parts of >= 256 rows, one CTA each, joined afterwards.  The cut
+            // a decoding row with a long context: its cache rows in 2..16 parts of >= 128 rows, one CTA each, joined afterwards.  The cut
             // depends on the row's position only.
-            int parts = (len == 1 && nq <= HY_MLA_TILE_QUERIES) ? std::min(16, (ctx - vis0) / 256) : 1;
+            int parts = (len == 1 && nq <= HY_MLA_TILE_QUERIES) ? std::min(16, (ctx - vis0) / 128) : 1;
             if (parts > 1 && next_slot + parts > split_slots_) parts = 1;
             if (parts > 1) {
                 const int per = ((ctx - vis0 + parts - 1) / parts + 31) / 32 * 32; parts = (ctx - vis0 + per - 1) / per;
@@ -950,7 +950,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
 }
 
 std::unique_ptr<ModelBase> make_model(const ModelConfig& cfg, const EngineOptions& opt) {
-    if (cfg.hybrid) return std::unique_ptr<ModelBase>(new HybridModel(cfg, opt));        // "ratasun", "zurevik": one class, configured by the design's traits
+    if (cfg.hybrid) return std::unique_ptr<ModelBase>(new HybridModel(cfg, opt));        // every design of the hybrid family: one class, configured by the design's traits
     if (opt.f32) throw std::runtime_error("the Llama-family models run in bf16 only; float32 is available for the hybrid family");
     return std::unique_ptr<ModelBase>(new DeviceModel(cfg, opt));
 }
