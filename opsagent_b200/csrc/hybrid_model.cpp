@@ -804,9 +804,10 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             tl.any_small = true;
             if (!tl.mma) continue;
             const int ctx = seq_pos0_[sq] + 1, vis0 = l.window > 0 ? std::max(0, ctx - l.window) / 32 * 32 : 0;       // first visible cache row of a decoding row, on a tile border
-            // a decoding row with a long context: its cache rows in 2..16 parts of >= 128 rows, one CTA each, joined afterwards.  The cut
-            // depends on the row's position only.
-            int parts = (len == 1 && nq <= HY_MLA_TILE_QUERIES) ? std::min(16, (ctx - vis0) / 128) : 1;
+            // a decoding row with a long context: its visible cache rows in 2..16 parts, one CTA each, joined afterwards — up to four parts of
+            // >= 128 rows, beyond that parts of >= 256 rows.  The cut depends on the row's position only.
+            const int vis = ctx - vis0;
+            int parts = (len == 1 && nq <= HY_MLA_TILE_QUERIES) ? std::min(16, std::max(vis / 256, std::min(4, vis / 128))) : 1;
             if (parts > 1 && next_slot + parts > split_slots_) parts = 1;
             if (parts > 1) {
                 const int per = ((ctx - vis0 + parts - 1) / parts + 31) / 32 * 32; parts = (ctx - vis0 + per - 1) / per;
