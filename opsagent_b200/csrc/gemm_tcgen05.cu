@@ -33,8 +33,9 @@ struct GemmCfg {
     static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;              // 16 KB
     static constexpr int B_BYTES = BN * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    // fill ~200 KB / (CTAs per SM we want): small tiles keep several CTAs resident
-    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 4 : 4));
+    // fill ~200 KB of shared memory.  The narrow tiles serve decoding steps (a few rows, at most one CTA per SM): what bounds them is the
+    // weight bytes a CTA has in flight, 4 or 8 KB per stage, so they take as many stages as fit
+    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 8 : 10));
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
     static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
 };

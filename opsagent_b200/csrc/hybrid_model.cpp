@@ -624,12 +624,11 @@ void HybridModel::window_mixer(const HyRun& run, const HyLayer& l, const LayerW&
                                const void* gate, int ldg, bool prepared) {
     HyWinAttn a{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, w.lambda, 1.f - l.diff};
     if (l.v_rot) { a.out_rot = l.rot_layout == HY_ROT_HALVES ? 2 : 1; a.out_cos = ropes_[w.rope_v].cos; a.out_sin = ropes_[w.rope_v].sin; }
-    if (prepared) {}
-    else if (l.rot_dims > 0 || l.v_rot) {
+    if (!prepared && (l.rot_dims > 0 || l.v_rot)) {
         const HyRotary rot{l.rot_dims, l.rot_layout, l.rot_dims > 0 ? ropes_[w.rope].cos : nullptr, l.rot_dims > 0 ? ropes_[w.rope].sin : nullptr,
                            l.v_rot ? ropes_[w.rope_v].cos : nullptr, l.v_rot ? ropes_[w.rope_v].sin : nullptr};
         cuda_check(hy_win_rope_prep(f32_, a, rot, q, ld, k, v, ld, caches_[run.cache_idx], r, stream), "rotary + cache write");
-    } else cuda_check(hy_win_prep(f32_, a, q, ld, k, v, ld, w.q_norm, w.k_norm, hc_.eps, caches_[run.cache_idx], r, stream), "query / key norm + cache write");
+    } else if (!prepared) cuda_check(hy_win_prep(f32_, a, q, ld, k, v, ld, w.q_norm, w.k_norm, hc_.eps, caches_[run.cache_idx], r, stream), "query / key norm + cache write");
     if (!prepared) MARK(23);
     if (tl.mma) {
         cuda_check(hy_win_attention_mma(a, q, ld, caches_[run.cache_idx], w.sink, gate, ldg, mix_, ld_mix_, hc_.eps, r, d_meta_ + tl.o_wseq, d_meta_ + tl.o_wq0, tl.n_w, stream), "windowed attention (mma)");
@@ -847,9 +846,9 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     else { cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, hc_.loop_times > 0 ? x0_ : nullptr, T, W, V, hc_.embed_scale, stream, hc_.post_norm ? h_ : nullptr, Wld_), "embed"); MARK(0); }
     auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
     for (const HyRun& run : hc_.runs) {
-        if (hc_.sequential) break;
+        if (hc_.sequential) break;          // forward_sequential() has run every layer execution
         const HyLayer& l = hc_.layers[run.layer]; const LayerW& w = lw_[run.layer];
-        if (run.first_of_pass) {         // re-injection: x <- W_in [x ; x0] + step[pass]
+        if (run.first_of_pass && hc_.loop_reinject) {         // re-injection: x <- W_in [x ; x0] + step[pass]
             cuda_check(hy_concat(f32_, x_, x0_, cat_, T, W, stream), "concat");
             gemm(HY_STORE_F32, cat_, 2 * W, loop_in_, x_, W, T, loop_step_ + (size_t)run.pass * W, 1.f); MARK(14);
         }

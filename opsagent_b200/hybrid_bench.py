@@ -75,13 +75,13 @@ def gosavik_sizes(name: str) -> dict:
     attention) of sizes(name), with a dense feed-forward of the Llama case's size, four residual streams, windows of 512 and YaRN-scaled rotary."""
     if name == "small":
         lat = {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "q_rank": 384, "scale": 96 ** -0.5}
-        att = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64, "conv": 4, "scale": 64 ** -0.5, "rot": {"base": 500000.0, "dims": 64}}
+        att = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64, "conv": 4, "scale": 64 ** -0.5, "rot": {"base": 1000000.0, "dims": 64}}
         width, ff = 1024, 2048
     else:
         lat = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 768, "scale": 192 ** -0.5}
-        att = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5, "rot": {"base": 500000.0, "dims": 128}}
+        att = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5, "rot": {"base": 1000000.0, "dims": 128}}
         width, ff = 2048, 4096
-    lat.update(mask={"size": 512}, rot={"base": 10000.0, "dims": lat["rot_dim"], "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}})
+    lat.update(mask={"size": 512}, rot={"base": 10000.0, "dims": lat["rot_dim"], "scaling": {"factor": 4.0, "original": 2048, "fast": 24.0, "slow": 2.0}})
     mlp = {"kind": "dense", "ff": ff}
     order = [("latent_attention", lat), ("attention", att), ("latent_attention", lat), ("attention", att)]
     return {"architecture": "Gosavik", "width": width, "vocab": 32000, "norm": {"eps": 1e-5}, "streams": 4, "loop": {"start": 1, "stop": 3, "times": 2},
