@@ -199,7 +199,14 @@ __global__ void __launch_bounds__(128) hy_conv_rope_cache_kernel(HyWinAttn a, Hy
                                                                  const float* __restrict__ w, __nv_bfloat16* __restrict__ q_out, int ldq, __nv_bfloat16* __restrict__ cache,
                                                                  const __nv_bfloat16* __restrict__ tails, HyRows r) {
     HY_PDL();
+    // the block's row metadata once, in shared memory: a thread's per-row chain is then one global load (its 16 bytes of input, requested a row ahead)
+    __shared__ int s_row0[ROWS], s_pos0[ROWS], s_pos[ROWS], s_slot[ROWS], s_state[ROWS];
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8, t0 = blockIdx.y * ROWS;
+    if (threadIdx.x < ROWS && t0 + threadIdx.x < r.T) {
+        const int t = t0 + threadIdx.x, seq = r.row_seq[t];
+        s_row0[threadIdx.x] = r.seq_row0[seq]; s_pos0[threadIdx.x] = r.seq_pos0[seq]; s_pos[threadIdx.x] = r.positions[t]; s_slot[threadIdx.x] = r.slots[t]; s_state[threadIdx.x] = r.seq_state[seq];
+    }
+    __syncthreads();
     const int D = a.dim, VD = a.vdim, KW = a.kv_heads * D, CW = KW + a.kv_heads * VD;
     int seg, local;                                      // 0: query, 1: key, 2: value; channel within the segment
     if (c >= off_q && c < off_q + a.heads * D) { seg = 0; local = c - off_q; }
@@ -219,11 +226,19 @@ __global__ void __launch_bounds__(128) hy_conv_rope_cache_kernel(HyWinAttn a, Hy
 #pragma unroll
         for (int i = 0; i < 4; ++i) { f[2 * i] = bf16lo(x[i]); f[2 * i + 1] = bf16hi(x[i]); }
     };
-    for (int tt = 0; tt < ROWS && t0 + tt < r.T; ++tt) {
-        const int t = t0 + tt, seq = r.row_seq[t], row0 = r.seq_row0[seq], i = t - row0;
+    constexpr int AHEAD = ROWS >= 4 ? 4 : 1;             // input rows requested ahead of the one being computed
+    uint4 ring[AHEAD];
+#pragma unroll
+    for (int k = 0; k < AHEAD; ++k) if (t0 + k < r.T) ring[k] = *reinterpret_cast<const uint4*>(in + (long long)(t0 + k) * ld_in + c);
+#pragma unroll
+    for (int tt = 0; tt < ROWS; ++tt) {
+        if (t0 + tt >= r.T) break;
+        const int t = t0 + tt, row0 = s_row0[tt], i = t - row0;
+        const uint4 cur = ring[tt % AHEAD];
+        if (tt + AHEAD < ROWS && t + AHEAD < r.T) ring[tt % AHEAD] = *reinterpret_cast<const uint4*>(in + (long long)(t + AHEAD) * ld_in + c);
         if (tt == 0 || i == 0) {
-            const int pos0 = r.seq_pos0[seq];
-            const __nv_bfloat16* tail = tails + (long long)r.seq_state[seq] * (TAPS - 1) * C;
+            const int pos0 = s_pos0[tt];
+            const __nv_bfloat16* tail = tails + (long long)s_state[tt] * (TAPS - 1) * C;
 #pragma unroll
             for (int j = 0; j < TAPS - 1; ++j) {
                 const int src = i - (TAPS - 1) + j;
@@ -233,7 +248,7 @@ __global__ void __launch_bounds__(128) hy_conv_rope_cache_kernel(HyWinAttn a, Hy
                 unpack(u, win[j]);
             }
         }
-        unpack(*reinterpret_cast<const uint4*>(in + (long long)t * ld_in + c), win[TAPS - 1]);
+        unpack(cur, win[TAPS - 1]);
         float y[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -242,7 +257,7 @@ __global__ void __launch_bounds__(128) hy_conv_rope_cache_kernel(HyWinAttn a, Hy
             for (int j = 0; j < TAPS; ++j) acc = fmaf(wr[j][e], win[j][e], acc);
             y[e] = acc;
         }
-        const long long pos = r.positions[t];
+        const long long pos = s_pos[tt];
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
             const int d = d0 + 2 * p;
@@ -252,7 +267,7 @@ __global__ void __launch_bounds__(128) hy_conv_rope_cache_kernel(HyWinAttn a, Hy
             }
         }
         const uint4 o = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
-        __nv_bfloat16* dst = seg == 0 ? q_out + (long long)t * ldq + local : cache + (long long)r.slots[t] * CW + (seg == 1 ? local : KW + local);
+        __nv_bfloat16* dst = seg == 0 ? q_out + (long long)t * ldq + local : cache + (long long)s_slot[tt] * CW + (seg == 1 ? local : KW + local);
         *reinterpret_cast<uint4*>(dst) = o;
 #pragma unroll
         for (int j = 0; j < TAPS - 1; ++j)
