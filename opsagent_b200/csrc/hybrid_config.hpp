@@ -2,7 +2,7 @@
 // attention (a compressed key/value cache), a gated delta rule with per-channel decay, a Mamba-2 state-space layer, or windowed attention
 // over cached keys and values (sliding window with optional kept first tokens, one or two score maps per head, optional sink, output gate,
 // optionally reading another layer's cache), each beside a routed mixture-of-experts feed-forward, with an optional looped block that
-// re-injects the embedding.  Three designs are registered: "Ratasun" (one weight-only layer norm per layer, sigmoid group-limited router, SwiGLU
+// re-injects the embedding.  Four designs are registered: "Ratasun" (one weight-only layer norm per layer, sigmoid group-limited router, SwiGLU
 // experts), "Zurevik" (two RMS norms per layer, softmax over the chosen router logits, squared-ReLU experts, scaled embedding, soft-capped
 // logits) and "Rofizen" (norm after the sum: x <- norm(alpha x + sublayer(x)), mixer and feed-forward in sequence; mixers: gated linear
 // attention with a decay per key channel, retention with a fixed decay per head and rotate-half rotary, or causal soft-capped attention with
